@@ -13,7 +13,9 @@ What is here instead:
   group has a page pool of its own and one tensor
   ``[entries, pages, 2 (K,V), kv_heads, page_size, head_dim]``; a page id is
   valid for every entry of its group.  A request has one block table per
-  group.
+  group.  A mixer that caches one vector per token (``PagedVectorNeed``: a
+  latent that keys and values are derived from) joins a group of its width
+  and window, whose tensor is ``[entries, pages, page_size, width]``.
 * **Pages on demand.**  ``append`` allocates the pages that the tokens of the
   coming step need, in all groups or in none; ``commit`` advances the
   request's length after the step has run (the reference's two-phase
@@ -47,16 +49,21 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..parts.registry import PagedKVNeed, StateNeed
+from ..parts.registry import PagedKVNeed, PagedVectorNeed, StateNeed
 from .pools import OutOfPages, PagePool, StateSlotPool
 
 
 @dataclass
 class CacheGroup:
-    need: PagedKVNeed
+    need: object                       # PagedKVNeed or PagedVectorNeed
     entries: List[int]                 # schedule-entry indices, in order
     pool: PagePool
-    kv: Optional[torch.Tensor] = None  # [entries, pages, 2, kv_heads, page_size, head_dim]
+    kv: Optional[torch.Tensor] = None  # [entries, pages, 2, kv_heads, page_size, head_dim], or [entries, pages, page_size, width]
+
+    def token_elements(self) -> int:
+        """Numbers cached per token and entry."""
+        n = self.need
+        return n.width if isinstance(n, PagedVectorNeed) else 2 * n.kv_heads * n.head_dim
 
 
 class PageList:
@@ -132,7 +139,7 @@ class RequestCache:
 @dataclass
 class PagedCacheView:
     """What a mixer sees of the paged cache in one step."""
-    kv: torch.Tensor                   # [pages, 2, kv_heads, page_size, head_dim] of one entry
+    kv: torch.Tensor                   # of one entry: [pages, 2, kv_heads, page_size, head_dim], or [pages, page_size, width]
     block_table: torch.Tensor          # int32 [R, width] of the entry's group, for this step
     slot_mapping: torch.Tensor         # int32 [T]: page * page_size + offset where each row's K/V goes
     page_size: int
@@ -163,8 +170,9 @@ class CacheManager:
         self.state_tensors: Dict[int, torch.Tensor] = {}
         by_key: Dict[Tuple, int] = {}
         for e, need in enumerate(needs):
-            if isinstance(need, PagedKVNeed):
-                key = (need.kv_heads, need.head_dim, need.window)
+            if isinstance(need, (PagedKVNeed, PagedVectorNeed)):
+                key = (("vector", need.width, need.window) if isinstance(need, PagedVectorNeed)
+                       else (need.kv_heads, need.head_dim, need.window))
                 if key not in by_key:
                     by_key[key] = len(self.groups)
                     self.groups.append(CacheGroup(need, [], PagePool(num_pages)))
@@ -185,15 +193,16 @@ class CacheManager:
         if allocate_tensors:
             for grp in self.groups:
                 n = grp.need
-                grp.kv = torch.zeros((len(grp.entries), num_pages, 2, n.kv_heads, page_size, n.head_dim),
-                                     dtype=dtype, device=device)
+                shape = ((num_pages, page_size, n.width) if isinstance(n, PagedVectorNeed)
+                         else (num_pages, 2, n.kv_heads, page_size, n.head_dim))
+                grp.kv = torch.zeros((len(grp.entries),) + shape, dtype=dtype, device=device)
         self.slots = StateSlotPool(max_requests)
         self.requests: Dict[Hashable, RequestCache] = {}
 
     # -- sizes ----------------------------------------------------------------
     def bytes_per_token(self) -> int:
         esize = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.entries) * 2 * g.need.kv_heads * g.need.head_dim * esize for g in self.groups)
+        return sum(len(g.entries) * g.token_elements() * esize for g in self.groups)
 
     # -- requests -------------------------------------------------------------
     def add_request(self, rid: Hashable) -> RequestCache:

@@ -38,7 +38,8 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--page-size", type=int, default=DEFAULT_PAGE_SIZE)
-    ap.add_argument("--max-requests", type=int, default=64)
+    ap.add_argument("--max-requests", type=int, default=4,
+                    help="requests that may be live at a time (state slots of mixers that carry a state)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
     if args.max_tokens < 1:

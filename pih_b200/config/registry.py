@@ -40,8 +40,11 @@ def config_class_for(name: str) -> type:
 
 def config_from_dict(raw: dict):
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]               # some designs name themselves with one string
     if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
-        raise ValueError("config.json: 'architectures' must be a list with exactly one name")
+        raise ValueError("config.json: 'architectures' must be a list with exactly one name "
+                         "(or 'architecture' one name)")
     return config_class_for(archs[0]).from_dict(raw)
 
 

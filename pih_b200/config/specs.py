@@ -74,15 +74,99 @@ class SwiGLUSpec:
 
 
 @dataclass(frozen=True)
+class ScalarNormSpec:
+    """RMS norm whose weight is ONE number for all coordinates (a tensor without axes)."""
+    width: int
+    eps: float
+    kind: str = "scalar_rmsnorm"
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """Gated delta rule: a matrix state ``S [key_dim, value_dim]`` per head that decays, is corrected towards the
+    new value along the new key, and is read with the query.  q and k have ``kv_heads`` heads shared by groups of
+    value heads; q, k and v pass a short causal convolution and SiLU; q and k are made unit vectors."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    norm_eps: float                   # of the per-head RMS norm of the read-out
+    unit_eps: float = 1e-6            # inside the root of the unit norm of q and k
+    kind: str = "gated_delta"
+    names: Mapping[str, str] = _names(q="mix.q", k="mix.k", v="mix.v", q_conv="mix.q.conv", k_conv="mix.k.conv",
+                                      v_conv="mix.v.conv", beta="mix.b", decay="mix.a", decay_log="mix.A_log",
+                                      decay_bias="mix.dt_bias", out_norm="mix.norm", gate="mix.g", o="mix.o")
+
+    @property
+    def qk_size(self) -> int:
+        return self.kv_heads * self.key_dim
+
+    @property
+    def v_size(self) -> int:
+        return self.heads * self.value_dim
+
+
+@dataclass(frozen=True)
+class RGLRUSpec:
+    """Recurrent block with a real-gated linear recurrent unit: a GELU branch and a branch of convolution and a
+    diagonal recurrence whose decay ``a = exp(-decay_scale * r * softplus(lam))`` and input gate come from
+    block-diagonal projections (``blocks`` square blocks) of the convolution's output."""
+    hidden: int
+    width: int
+    blocks: int
+    conv_taps: int
+    decay_scale: float = 8.0
+    kind: str = "rglru"
+    names: Mapping[str, str] = _names(y="mix.y", y_bias="mix.y.b", x="mix.x", x_bias="mix.x.b", conv="mix.conv",
+                                      conv_bias="mix.conv.b", r="mix.ra", r_bias="mix.ra.b", i="mix.ri",
+                                      i_bias="mix.ri.b", lam="mix.lam", o="mix.o")
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention whose keys and values are up-projections of one cached latent vector per token
+    (``latent_rank`` numbers, RMS-normed), without positions; the softmax denominator may hold a learned
+    per-head sink, and a per-head sigmoid gate may multiply the head's output."""
+    hidden: int
+    heads: int
+    key_dim: int
+    value_dim: int
+    latent_rank: int
+    scale: float
+    norm_eps: float
+    sink: bool = True
+    gated: bool = True
+    kind: str = "latent_attention"
+    names: Mapping[str, str] = _names(q="mix.q", down="mix.dkv", down_norm="mix.dkv.norm", up_k="mix.uk",
+                                      up_v="mix.uv", sink="mix.sink", gate="mix.g", o="mix.o")
+
+
+@dataclass(frozen=True)
+class MoESpec:
+    """Mixture of gated feed-forward experts: the ``top`` largest router logits choose, the softmax over the
+    chosen logits weighs.  ``names["expert"]`` is formatted with the expert's index."""
+    hidden: int
+    experts: int
+    top: int
+    intermediate: int
+    activation: str = "silu"
+    kind: str = "moe"
+    names: Mapping[str, str] = _names(router="mlp.router", expert="mlp.e{}.", gate="gate", up="up", down="down")
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: ``h += mixer(norm_in(h)); h += ffn(norm_post(h))`` for
-    ``arrangement == "prenorm"``.  ``prefix`` is the layer's tensor-name
-    prefix in the weight files."""
+    ``arrangement == "prenorm"``; ``ffn`` and ``norm_post`` None: the layer has
+    no feed-forward.  ``prefix`` is the layer's tensor-name prefix in the
+    weight files."""
     prefix: str
     mixer: object
-    ffn: object
-    norm_in: NormSpec
-    norm_post: NormSpec
+    ffn: Optional[object]
+    norm_in: object
+    norm_post: Optional[object]
     arrangement: str = "prenorm"
     names: Mapping[str, str] = _names(norm_in="input_layernorm.",
                                       norm_post="post_attention_layernorm.")
@@ -103,13 +187,16 @@ class ModelSpec:
     hidden: int
     blocks: Sequence[BlockSpec]
     schedule: Sequence[ScheduleEntry]
-    final_norm: NormSpec
+    final_norm: object
     tie_embeddings: bool
     embed_name: str = "model.embed_tokens.weight"
     final_norm_prefix: str = "model.norm."
     head_name: str = "lm_head.weight"
     max_positions: int = 0
     eos_token_ids: Sequence[int] = field(default_factory=tuple)
+    # "float32": the residual stream is kept and summed in 32-bit whatever the compute dtype (norms read it and
+    # give the compute dtype); None: the stream has the compute dtype
+    stream_dtype: Optional[str] = None
 
     def validate(self) -> None:
         for i, e in enumerate(self.schedule):

@@ -21,9 +21,14 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 template <typename TA, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, TC* __restrict__ C, int M, int N,
-                 int K, long long lda, long long ldw, long long ldc) {
+                 int K, long long lda, long long ldw, long long ldc, long long batch_a, long long batch_w,
+                 long long batch_c) {
   wait_for_prior_kernels();
   launch_dependents();                                   // (the next kernel's blocks may become resident and wait)
+  // blockIdx.z: one of several products of the same shape (a head, a diagonal block), operands apart by the strides
+  A += blockIdx.z * batch_a;
+  W += blockIdx.z * batch_w;
+  C += blockIdx.z * batch_c;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -86,27 +91,36 @@ gemm_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, TC* __restr
 
 using namespace pih;
 
-extern "C" int pih_gemm_simt(int in_dtype, int out_dtype, const void* A, const void* W, void* C, int M,
-                             int N, int K, long long lda, long long ldw, long long ldc, void* stream) {
-  if (M <= 0 || N <= 0) return 0;
+// ``batches`` products C_b[M,N] = A_b[M,K] . W_b[N,K]^T in one launch: operand b starts ``batch_*`` elements behind
+// operand b-1 (rows of A_b may interleave with those of other batches: lda is free).  The same kernel, hence the same
+// rounding, as the single product.
+extern "C" int pih_gemm_simt_batched(int in_dtype, int out_dtype, const void* A, const void* W, void* C, int M,
+                                     int N, int K, long long lda, long long ldw, long long ldc, int batches,
+                                     long long batch_a, long long batch_w, long long batch_c, void* stream) {
+  if (M <= 0 || N <= 0 || batches <= 0) return 0;
   if (K <= 0) return PIH_ERR_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  if (grid.y > 65535) return PIH_ERR_UNSUPPORTED;
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batches);
+  if (grid.y > 65535 || grid.z > 65535) return PIH_ERR_UNSUPPORTED;
   if (in_dtype == PIH_F32 && out_dtype == PIH_F32)
     launch_kernel(gemm_simt_kernel<float, float>, dim3(grid), dim3(256), 0, s, static_cast<const float*>(A),
                                                         static_cast<const float*>(W),
-                                                        static_cast<float*>(C), M, N, K, lda, ldw, ldc);
+                                                        static_cast<float*>(C), M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
   else if (in_dtype == PIH_BF16 && out_dtype == PIH_BF16)
     launch_kernel(gemm_simt_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(256), 0, s, 
         static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(W),
-        static_cast<__nv_bfloat16*>(C), M, N, K, lda, ldw, ldc);
+        static_cast<__nv_bfloat16*>(C), M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
   else if (in_dtype == PIH_BF16 && out_dtype == PIH_F32)
     launch_kernel(gemm_simt_kernel<__nv_bfloat16, float>, dim3(grid), dim3(256), 0, s, 
         static_cast<const __nv_bfloat16*>(A), static_cast<const __nv_bfloat16*>(W),
-        static_cast<float*>(C), M, N, K, lda, ldw, ldc);
+        static_cast<float*>(C), M, N, K, lda, ldw, ldc, batch_a, batch_w, batch_c);
   else
     return PIH_ERR_BAD_ARGUMENT;
   PIH_LAUNCH_CHECK();
   return 0;
+}
+
+extern "C" int pih_gemm_simt(int in_dtype, int out_dtype, const void* A, const void* W, void* C, int M,
+                             int N, int K, long long lda, long long ldw, long long ldc, void* stream) {
+  return pih_gemm_simt_batched(in_dtype, out_dtype, A, W, C, M, N, K, lda, ldw, ldc, 1, 0, 0, 0, stream);
 }

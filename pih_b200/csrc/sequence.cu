@@ -1,0 +1,441 @@
+// Kernels of mixers that carry a state from token to token, and of a residual stream kept in 32-bit.
+//
+//   embedding_stream      table rows (bf16 or fp32) -> a 32-bit stream
+//   rmsnorm_stream        h (fp32) += delta; out = h / sqrt(mean(h^2) + eps) * w, w a vector or ONE number
+//   causal_conv           short causal convolution per channel over each request's rows, the last taps-1 inputs
+//                         carried in the request's state slot
+//   delta_prepare         unit-norm q and k per head, decay and write strength per head (32-bit)
+//   delta_recurrence      gated delta rule: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q
+//   gated_rmsnorm         per-head RMS norm of the read-out, times a weight, times silu(gate)
+//   rglru_scan            real-gated linear recurrent unit: S <- a S + sqrt(1 - a^2) (i u), out = S * gelu(y)
+//
+// A step's rows are packed: request r owns rows cu_q[r] .. cu_q[r+1]-1 in the order of their positions, and
+// state_slots[r] is its slot in the state tensor (fp32, ``state_stride`` numbers a slot).  Kernels that carry state
+// are driven by requests, so rows of padding (no request) are never touched and requests of padding (no rows, slot -1)
+// do nothing.  Everything that enters a recurrence is 32-bit: states, decays, gates, unit norms; only the inputs that
+// come from projections and convolutions have the storage type T.  A request's result depends on its own rows and
+// state alone, in an order of operations fixed by the row: cutting a prompt or batching it changes no bit.
+#include "common.cuh"
+
+namespace pih {
+
+constexpr int kMaxTaps = 16;
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.0f) + log1pf(expf(-fabsf(x))); }
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename T>
+__global__ void embedding_stream_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
+                                        int hidden, int vocab, uint32_t* err) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int row = blockIdx.x;
+  int id = ids[row];
+  const bool bad = id < 0 || id >= vocab;
+  if (bad) {
+    if (threadIdx.x == 0) publish_error(err, kTokenOutOfVocabulary);
+    id = 0;
+  }
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+    out[static_cast<long long>(row) * hidden + c] = bad ? 0.0f : to_float<T>(table[static_cast<long long>(id) * hidden + c]);
+}
+
+// One block a row.  Without ``rows``: h[row] += delta[row] is stored back and normed.  With ``rows`` (a gather of the
+// rows whose logits are wanted) nothing is stored: the sum is formed for the norm alone.
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256)
+rmsnorm_stream_kernel(float* __restrict__ h, const TD* __restrict__ delta, const float* __restrict__ weight, int weight_len,
+                      TO* __restrict__ out, const int* __restrict__ rows, int width, float eps) {
+  __shared__ float scratch[33];
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int row = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
+  float* hr = h + static_cast<long long>(row) * width;
+  const TD* dr = delta != nullptr ? delta + static_cast<long long>(row) * width : nullptr;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float v = hr[c];
+    if (dr != nullptr) {
+      v += to_float<TD>(dr[c]);
+      if (rows == nullptr) hr[c] = v;
+    }
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float scale = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+  TO* o = out + static_cast<long long>(blockIdx.x) * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float v = hr[c];
+    if (dr != nullptr && rows != nullptr) v += to_float<TD>(dr[c]);
+    o[c] = from_float<TO>(v * scale * (weight_len == 1 ? weight[0] : weight[c]));
+  }
+}
+
+// Block (32 channels, 8 token lanes) owns a request's rows of 32 channels: it reads the old history, computes every
+// row, and its first token lane writes the new history at the end (no other block touches these numbers).
+// in(s) = x[s] + in_bias for s >= 0, the history for -(taps-1) <= s < 0 (zeros at the start of a sequence).
+// out[t] = act( sum_j w[c][j] in(t - (taps-1) + j) + out_bias ).
+template <typename T>
+__global__ void __launch_bounds__(256)
+causal_conv_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w, const float* __restrict__ in_bias,
+                   const float* __restrict__ out_bias, T* __restrict__ out, long long ldo, int channels, int taps,
+                   int activation, float* __restrict__ state, long long state_stride, long long state_offset,
+                   const int* __restrict__ cu_q, const int* __restrict__ state_slots) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int r = blockIdx.x;
+  const int c = blockIdx.y * 32 + threadIdx.x;
+  const int lo = cu_q[r], n = cu_q[r + 1] - lo;
+  const int slot = state_slots[r];
+  if (n <= 0 || slot < 0) return;
+  const bool live = c < channels;
+  const int hist_n = taps - 1;
+  float* st = state + slot * state_stride + state_offset;       // [taps-1][channels]
+  __shared__ float hist[kMaxTaps][32];
+  float wr[kMaxTaps];
+#pragma unroll
+  for (int j = 0; j < kMaxTaps; ++j)
+    wr[j] = (live && j < taps) ? to_float<T>(w[static_cast<long long>(c) * taps + j]) : 0.0f;
+  if (threadIdx.y == 0)
+    for (int j = 0; j < hist_n; ++j) hist[j][threadIdx.x] = live ? st[static_cast<long long>(j) * channels + c] : 0.0f;
+  const float ib = (live && in_bias != nullptr) ? in_bias[c] : 0.0f;
+  const float ob = (live && out_bias != nullptr) ? out_bias[c] : 0.0f;
+  __syncthreads();                                              // the old history is on chip
+  if (!live) return;
+  auto input = [&](int s) -> float {
+    return s >= 0 ? to_float<T>(x[static_cast<long long>(lo + s) * ldx + c]) + ib : hist[hist_n + s][threadIdx.x];
+  };
+  for (int t = threadIdx.y; t < n; t += blockDim.y) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j)
+      if (j < taps) acc = fmaf(wr[j], input(t - hist_n + j), acc);
+    acc += ob;
+    if (activation == 1) acc = acc / (1.0f + expf(-acc));
+    out[static_cast<long long>(lo + t) * ldo + c] = from_float<T>(acc);
+  }
+  if (threadIdx.y == 0)
+    for (int j = 0; j < hist_n; ++j) st[static_cast<long long>(j) * channels + c] = input(n - hist_n + j);
+}
+
+// One block a row.  qk: [rows, ld] with q heads at column 0 and k heads at column kv_heads*dim (after convolution and
+// activation); ba: [rows, ldb] with the write-strength logits at column 0 and the decay logits at column ``heads``.
+// qn, kn: fp32 [rows, kv_heads, dim]; decay, beta: fp32 [rows, heads].
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(const T* __restrict__ qk, long long ld, const T* __restrict__ ba, long long ldb,
+                     const float* __restrict__ decay_log, const float* __restrict__ decay_bias, float* __restrict__ qn,
+                     float* __restrict__ kn, float* __restrict__ decay, float* __restrict__ beta, int heads, int kv_heads,
+                     int dim, float unit_eps, float q_scale) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  for (int v = warp; v < 2 * kv_heads; v += warps) {             // vector v: q head v, or k head v - kv_heads
+    const T* src = qk + static_cast<long long>(row) * ld + static_cast<long long>(v) * dim;
+    float ss = 0.0f;
+    for (int i = lane; i < dim; i += 32) { const float a = to_float<T>(src[i]); ss = fmaf(a, a, ss); }
+    ss = warp_sum(ss);
+    const float scale = (1.0f / sqrtf(ss + unit_eps)) * (v < kv_heads ? q_scale : 1.0f);
+    float* dst = (v < kv_heads ? qn : kn) + (static_cast<long long>(row) * kv_heads + (v < kv_heads ? v : v - kv_heads)) * dim;
+    for (int i = lane; i < dim; i += 32) dst[i] = to_float<T>(src[i]) * scale;
+  }
+  for (int h = threadIdx.x; h < heads; h += blockDim.x) {
+    const float b = to_float<T>(ba[static_cast<long long>(row) * ldb + h]);
+    const float a = to_float<T>(ba[static_cast<long long>(row) * ldb + heads + h]);
+    beta[static_cast<long long>(row) * heads + h] = sigmoid_f(b);
+    decay[static_cast<long long>(row) * heads + h] = expf(-expf(decay_log[h]) * softplus_f(a + decay_bias[h]));
+  }
+}
+
+// Block (request, head, slice of value columns); thread j owns column v0 + j of S (all ``dim`` rows, in shared memory:
+// S[i][j], conflict-free).  The next token's k and q are fetched into registers while this token is computed.
+template <typename T>
+__global__ void delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const T* __restrict__ v,
+                                        long long ldv, const float* __restrict__ decay, const float* __restrict__ beta,
+                                        float* __restrict__ out, float* __restrict__ state, long long state_stride,
+                                        const int* __restrict__ cu_q, const int* __restrict__ state_slots, int heads,
+                                        int kv_heads, int dim, int vdim) {
+  extern __shared__ float smem[];
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int cols = blockDim.x;
+  const int j = threadIdx.x, col = blockIdx.z * cols + j;
+  const int lo = cu_q[r], hi = cu_q[r + 1];
+  const int slot = state_slots[r];
+  if (hi <= lo || slot < 0) return;
+  const int kh = h / (heads / kv_heads);
+  float* S = smem;                          // [dim][cols]
+  float* kq = smem + dim * cols;            // [2 buffers][k: dim | q: dim]
+  const bool live = col < vdim;
+  float* Sg = state + slot * state_stride + (static_cast<long long>(h) * dim) * vdim;
+  for (int i = 0; i < dim; ++i) S[i * cols + j] = live ? Sg[static_cast<long long>(i) * vdim + col] : 0.0f;
+  const int per = (2 * dim + cols - 1) / cols;                   // numbers of k|q a thread fetches
+  auto fetch = [&](int t, int e) -> float {
+    const int idx = j + e * cols;
+    if (idx >= 2 * dim) return 0.0f;
+    const float* src = idx < dim ? kn : qn;
+    return src[(static_cast<long long>(t) * kv_heads + kh) * dim + (idx < dim ? idx : idx - dim)];
+  };
+  constexpr int kMaxPer = 16;               // dim <= 8 * cols
+  float nxt[kMaxPer];
+#pragma unroll
+  for (int e = 0; e < kMaxPer; ++e) nxt[e] = e < per ? fetch(lo, e) : 0.0f;
+  for (int t = lo; t < hi; ++t) {
+    float* cur = kq + (t & 1) * 2 * dim;
+#pragma unroll
+    for (int e = 0; e < kMaxPer; ++e)
+      if (e < per && j + e * cols < 2 * dim) cur[j + e * cols] = nxt[e];
+    __syncthreads();
+    if (t + 1 < hi) {
+#pragma unroll
+      for (int e = 0; e < kMaxPer; ++e) nxt[e] = e < per ? fetch(t + 1, e) : 0.0f;
+    }
+    const float g = decay[static_cast<long long>(t) * heads + h];
+    const float b = beta[static_cast<long long>(t) * heads + h];
+    const float vj = live ? to_float<T>(v[static_cast<long long>(t) * ldv + static_cast<long long>(h) * vdim + col]) : 0.0f;
+    const float* k = cur;
+    const float* q = cur + dim;
+    float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+    int i = 0;
+    for (; i + 4 <= dim; i += 4) {
+      a0 = fmaf(S[(i + 0) * cols + j], k[i + 0], a0);
+      a1 = fmaf(S[(i + 1) * cols + j], k[i + 1], a1);
+      a2 = fmaf(S[(i + 2) * cols + j], k[i + 2], a2);
+      a3 = fmaf(S[(i + 3) * cols + j], k[i + 3], a3);
+    }
+    for (; i < dim; ++i) a0 = fmaf(S[i * cols + j], k[i], a0);
+    const float u = b * (vj - g * ((a0 + a1) + (a2 + a3)));
+    float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+    i = 0;
+    for (; i + 4 <= dim; i += 4) {
+      const float s0 = fmaf(k[i + 0], u, g * S[(i + 0) * cols + j]);
+      const float s1 = fmaf(k[i + 1], u, g * S[(i + 1) * cols + j]);
+      const float s2 = fmaf(k[i + 2], u, g * S[(i + 2) * cols + j]);
+      const float s3 = fmaf(k[i + 3], u, g * S[(i + 3) * cols + j]);
+      S[(i + 0) * cols + j] = s0; S[(i + 1) * cols + j] = s1; S[(i + 2) * cols + j] = s2; S[(i + 3) * cols + j] = s3;
+      o0 = fmaf(s0, q[i + 0], o0); o1 = fmaf(s1, q[i + 1], o1); o2 = fmaf(s2, q[i + 2], o2); o3 = fmaf(s3, q[i + 3], o3);
+    }
+    for (; i < dim; ++i) {
+      const float s0 = fmaf(k[i], u, g * S[i * cols + j]);
+      S[i * cols + j] = s0;
+      o0 = fmaf(s0, q[i], o0);
+    }
+    if (live) out[(static_cast<long long>(t) * heads + h) * vdim + col] = (o0 + o1) + (o2 + o3);
+  }
+  if (live)
+    for (int i = 0; i < dim; ++i) Sg[static_cast<long long>(i) * vdim + col] = S[i * cols + j];
+}
+
+// One warp a (row, head): o fp32 [rows, heads, vdim]; gate [rows, ldg] with head h at column h * vdim.
+template <typename T>
+__global__ void __launch_bounds__(128)
+gated_rmsnorm_kernel(const float* __restrict__ o, const T* __restrict__ gate, long long ldg, const float* __restrict__ weight,
+                     T* __restrict__ out, long long rows_heads, int heads, int vdim, float eps) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= rows_heads) return;
+  const int lane = threadIdx.x & 31;
+  const long long row = item / heads;
+  const int h = static_cast<int>(item % heads);
+  const float* src = o + item * vdim;
+  float ss = 0.0f;
+  for (int i = lane; i < vdim; i += 32) ss = fmaf(src[i], src[i], ss);
+  ss = warp_sum(ss);
+  const float scale = 1.0f / sqrtf(ss / static_cast<float>(vdim) + eps);
+  const T* g = gate + row * ldg + static_cast<long long>(h) * vdim;
+  T* dst = out + item * vdim;
+  for (int i = lane; i < vdim; i += 32) {
+    const float z = to_float<T>(g[i]);
+    dst[i] = from_float<T>(src[i] * scale * weight[i] * (z / (1.0f + expf(-z))));
+  }
+}
+
+// Thread a (request, channel).  gates: fp32 [rows, blocks, 2 * bw]: block b's decay-gate logits, then its input-gate
+// logits (without their biases).  y_pre [rows, ldy]: the other branch before its bias and GELU.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rglru_scan_kernel(const T* __restrict__ u, long long ldu, const float* __restrict__ gates, const T* __restrict__ y_pre,
+                  long long ldy, const float* __restrict__ y_bias, const float* __restrict__ r_bias,
+                  const float* __restrict__ i_bias, const float* __restrict__ lam, float decay_scale, T* __restrict__ out,
+                  long long ldo, float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
+                  const int* __restrict__ state_slots, int width, int blocks) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int r = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int lo = cu_q[r], hi = cu_q[r + 1];
+  const int slot = state_slots[r];
+  if (hi <= lo || slot < 0 || c >= width) return;
+  const int bw = width / blocks, b = c / bw, o = c % bw;
+  float S = state[slot * state_stride + c];
+  const float rate = decay_scale * softplus_f(lam[c]);
+  const float rb = r_bias[c], ib = i_bias[c], yb = y_bias[c];
+  for (int t = lo; t < hi; ++t) {
+    const float* g = gates + (static_cast<long long>(t) * blocks + b) * (2 * bw);
+    const float rg = sigmoid_f(g[o] + rb);
+    const float ig = sigmoid_f(g[bw + o] + ib);
+    const float log_a = -rate * rg;
+    const float a = expf(log_a);
+    const float mult = sqrtf(-expm1f(2.0f * log_a));            // sqrt(1 - a^2) without the cancellation near a = 1
+    S = fmaf(a, S, mult * (ig * to_float<T>(u[static_cast<long long>(t) * ldu + c])));
+    const float y = gelu_tanh_f(to_float<T>(y_pre[static_cast<long long>(t) * ldy + c]) + yb);
+    out[static_cast<long long>(t) * ldo + c] = from_float<T>(S * y);
+  }
+  state[slot * state_stride + c] = S;
+}
+
+}  // namespace pih
+
+using namespace pih;
+typedef __nv_bfloat16 bf16;
+
+extern "C" int pih_embedding_stream(int dtype, const void* table, const void* ids, void* out, int rows, int hidden,
+                                    int vocab, void* err, void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int threads = hidden >= 256 ? 256 : 64;
+  if (dtype == PIH_F32)
+    launch_kernel(embedding_stream_kernel<float>, dim3(rows), dim3(threads), 0, s, static_cast<const float*>(table),
+                  static_cast<const int*>(ids), static_cast<float*>(out), hidden, vocab, static_cast<uint32_t*>(err));
+  else if (dtype == PIH_BF16)
+    launch_kernel(embedding_stream_kernel<bf16>, dim3(rows), dim3(threads), 0, s, static_cast<const bf16*>(table),
+                  static_cast<const int*>(ids), static_cast<float*>(out), hidden, vocab, static_cast<uint32_t*>(err));
+  else
+    return PIH_ERR_BAD_ARGUMENT;
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int pih_rmsnorm_stream(int delta_dtype, int out_dtype, void* h, const void* delta, const void* weight,
+                                  int weight_len, void* out, const void* rows, int n_out, int width, float eps,
+                                  void* stream) {
+  if (n_out <= 0) return 0;
+  if (weight_len != 1 && weight_len != width) return PIH_ERR_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int threads = width >= 1024 ? 256 : 128;
+#define PIH_NORM(TD, TO)                                                                                              \
+  launch_kernel(rmsnorm_stream_kernel<TD, TO>, dim3(n_out), dim3(threads), 0, s, static_cast<float*>(h),               \
+                static_cast<const TD*>(delta), static_cast<const float*>(weight), weight_len, static_cast<TO*>(out),   \
+                static_cast<const int*>(rows), width, eps)
+  if (delta_dtype == PIH_F32 && out_dtype == PIH_F32) PIH_NORM(float, float);
+  else if (delta_dtype == PIH_BF16 && out_dtype == PIH_BF16) PIH_NORM(bf16, bf16);
+  else if (delta_dtype == PIH_F32 && out_dtype == PIH_BF16) PIH_NORM(float, bf16);
+  else if (delta_dtype == PIH_BF16 && out_dtype == PIH_F32) PIH_NORM(bf16, float);
+  else return PIH_ERR_BAD_ARGUMENT;
+#undef PIH_NORM
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int pih_causal_conv(int dtype, const void* x, long long ldx, const void* w, const void* in_bias,
+                               const void* out_bias, void* out, long long ldo, int channels, int taps, int activation,
+                               void* state, long long state_stride, long long state_offset, const void* cu_q,
+                               const void* state_slots, int requests, void* stream) {
+  if (requests <= 0 || channels <= 0) return 0;
+  if (taps < 1 || taps > kMaxTaps) return PIH_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  dim3 grid(requests, (channels + 31) / 32), block(32, 8);
+  if (grid.y > 65535) return PIH_ERR_UNSUPPORTED;
+#define PIH_CONV(T)                                                                                                    \
+  launch_kernel(causal_conv_kernel<T>, grid, block, 0, s, static_cast<const T*>(x), ldx, static_cast<const T*>(w),      \
+                static_cast<const float*>(in_bias), static_cast<const float*>(out_bias), static_cast<T*>(out), ldo,    \
+                channels, taps, activation, static_cast<float*>(state), state_stride, state_offset,                   \
+                static_cast<const int*>(cu_q), static_cast<const int*>(state_slots))
+  if (dtype == PIH_F32) PIH_CONV(float);
+  else if (dtype == PIH_BF16) PIH_CONV(bf16);
+  else return PIH_ERR_BAD_ARGUMENT;
+#undef PIH_CONV
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+// The gated delta rule over a step's rows.  qkv [rows, ld]: q heads, k heads, v heads (after convolution and SiLU);
+// ba [rows, ldb]: write-strength logits, decay logits.  scratch: fp32, rows * (2 * kv_heads * dim + 2 * heads).
+// out: fp32 [rows, heads, vdim].  The state S [heads, dim, vdim] lies at the start of a request's slot.
+extern "C" int pih_gated_delta_rule(int dtype, const void* qkv, long long ld, const void* ba, long long ldb,
+                                    const void* decay_log, const void* decay_bias, void* scratch, void* out, void* state,
+                                    long long state_stride, const void* cu_q, const void* state_slots, int rows,
+                                    int requests, int heads, int kv_heads, int dim, int vdim, float unit_eps,
+                                    float q_scale, void* stream) {
+  if (rows <= 0 || requests <= 0) return 0;
+  if (heads % kv_heads) return PIH_ERR_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int cols = vdim >= 64 ? 64 : 32;
+  if (dim > 8 * cols) return PIH_ERR_UNSUPPORTED;
+  const size_t smem = (static_cast<size_t>(dim) * cols + 4 * static_cast<size_t>(dim)) * sizeof(float);
+  if (smem > 200 * 1024) return PIH_ERR_UNSUPPORTED;
+  float* qn = static_cast<float*>(scratch);
+  float* kn = qn + static_cast<long long>(rows) * kv_heads * dim;
+  float* decay = kn + static_cast<long long>(rows) * kv_heads * dim;
+  float* beta = decay + static_cast<long long>(rows) * heads;
+  dim3 grid(requests, heads, (vdim + cols - 1) / cols);
+  if (grid.y > 65535 || grid.z > 65535) return PIH_ERR_UNSUPPORTED;
+  const long long qk_size = static_cast<long long>(kv_heads) * dim;
+#define PIH_DELTA(T)                                                                                                   \
+  do {                                                                                                                 \
+    launch_kernel(delta_prepare_kernel<T>, dim3(rows), dim3(128), 0, s, static_cast<const T*>(qkv), ld,                \
+                  static_cast<const T*>(ba), ldb, static_cast<const float*>(decay_log),                                \
+                  static_cast<const float*>(decay_bias), qn, kn, decay, beta, heads, kv_heads, dim, unit_eps, q_scale); \
+    PIH_LAUNCH_CHECK();                                                                                                \
+    if (smem > 48 * 1024)                                                                                              \
+      cudaFuncSetAttribute(delta_recurrence_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+    launch_kernel(delta_recurrence_kernel<T>, grid, dim3(cols), smem, s, static_cast<const float*>(qn),                \
+                  static_cast<const float*>(kn), static_cast<const T*>(qkv) + 2 * qk_size, ld,                         \
+                  static_cast<const float*>(decay), static_cast<const float*>(beta), static_cast<float*>(out),         \
+                  static_cast<float*>(state), state_stride, static_cast<const int*>(cu_q),                             \
+                  static_cast<const int*>(state_slots), heads, kv_heads, dim, vdim);                                   \
+  } while (0)
+  if (dtype == PIH_F32) PIH_DELTA(float);
+  else if (dtype == PIH_BF16) PIH_DELTA(bf16);
+  else return PIH_ERR_BAD_ARGUMENT;
+#undef PIH_DELTA
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int pih_gated_rmsnorm(int dtype, const void* o, const void* gate, long long ldg, const void* weight, void* out,
+                                 int rows, int heads, int vdim, float eps, void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long items = static_cast<long long>(rows) * heads;
+  dim3 grid(static_cast<unsigned>((items + 3) / 4));
+#define PIH_GN(T)                                                                                                      \
+  launch_kernel(gated_rmsnorm_kernel<T>, grid, dim3(128), 0, s, static_cast<const float*>(o), static_cast<const T*>(gate), \
+                ldg, static_cast<const float*>(weight), static_cast<T*>(out), items, heads, vdim, eps)
+  if (dtype == PIH_F32) PIH_GN(float);
+  else if (dtype == PIH_BF16) PIH_GN(bf16);
+  else return PIH_ERR_BAD_ARGUMENT;
+#undef PIH_GN
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int pih_rglru_scan(int dtype, const void* u, long long ldu, const void* gates, const void* y_pre, long long ldy,
+                              const void* y_bias, const void* r_bias, const void* i_bias, const void* lam,
+                              float decay_scale, void* out, long long ldo, void* state, long long state_stride,
+                              const void* cu_q, const void* state_slots, int requests, int width, int blocks,
+                              void* stream) {
+  if (requests <= 0 || width <= 0) return 0;
+  if (blocks < 1 || width % blocks) return PIH_ERR_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  dim3 grid(requests, (width + 127) / 128);
+  if (grid.y > 65535) return PIH_ERR_UNSUPPORTED;
+#define PIH_SCAN(T)                                                                                                    \
+  launch_kernel(rglru_scan_kernel<T>, grid, dim3(128), 0, s, static_cast<const T*>(u), ldu,                            \
+                static_cast<const float*>(gates), static_cast<const T*>(y_pre), ldy, static_cast<const float*>(y_bias), \
+                static_cast<const float*>(r_bias), static_cast<const float*>(i_bias), static_cast<const float*>(lam),  \
+                decay_scale, static_cast<T*>(out), ldo, static_cast<float*>(state), state_stride,                      \
+                static_cast<const int*>(cu_q), static_cast<const int*>(state_slots), width, blocks)
+  if (dtype == PIH_F32) PIH_SCAN(float);
+  else if (dtype == PIH_BF16) PIH_SCAN(bf16);
+  else return PIH_ERR_BAD_ARGUMENT;
+#undef PIH_SCAN
+  PIH_LAUNCH_CHECK();
+  return 0;
+}

@@ -55,6 +55,8 @@ def cache_tokens_for_memory(model, *, page_size: int, max_requests: int, max_bat
     for entry, need in zip(spec.schedule, model.cache_needs()):
         if hasattr(need, "kv_heads"):
             per_token += 2 * need.kv_heads * need.head_dim * esize
+        elif hasattr(need, "width"):                               # one cached vector per token
+            per_token += need.width * esize
     for block in spec.blocks:
         mixer, ffn = block.mixer, block.ffn
         widest = max(widest, 4 * spec.hidden + 2 * getattr(mixer, "q_size", 0) + 3 * getattr(mixer, "kv_size", 0)

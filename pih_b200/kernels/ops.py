@@ -104,10 +104,14 @@ class CudaOps:
                      "pih_sample", "pih_selected_logprob", "pih_top_logprobs", "pih_paged_attention_mma", "pih_gemm_tcgen05", "pih_make_kv_tensor_map",
                      "pih_attention_prefill_tcgen05", "pih_gemm_skinny", "pih_set_dependent_launch", "pih_set_attention_cluster_merge",
                      "pih_gemm_skinny_f32out",
-                     "pih_qk_attention_fused", "pih_gemm_tcgen05_pair", "pih_set_attention_side_by_side", "pih_set_skinny_rule"):
+                     "pih_qk_attention_fused", "pih_gemm_tcgen05_pair", "pih_set_attention_side_by_side", "pih_set_skinny_rule",
+                     "pih_gemm_simt_batched", "pih_embedding_stream", "pih_rmsnorm_stream", "pih_causal_conv",
+                     "pih_gated_delta_rule", "pih_gated_rmsnorm", "pih_rglru_scan", "pih_latent_write",
+                     "pih_latent_attention_generic", "pih_moe_route", "pih_moe_experts"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
         lib.pih_top_logprobs_scratch_words.restype = c_ll
+        lib.pih_moe_route_words.restype = c_ll
 
     def _native_supports(self, block) -> bool:
         from .native_block import NativeBlocks
@@ -185,8 +189,16 @@ class CudaOps:
         return c_void_p(self._error.data_ptr())
 
     # -- ops ----------------------------------------------------------------------
-    def embedding(self, table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    def embedding(self, table: torch.Tensor, ids: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         rows, (vocab, hidden) = ids.shape[0], table.shape
+        if out_dtype is not None and out_dtype != table.dtype:
+            if out_dtype != torch.float32:
+                raise ValueError("an embedding widens to float32 only")
+            out = torch.empty(rows, hidden, dtype=torch.float32, device=table.device)      # a 32-bit residual stream
+            rc = self.lib.pih_embedding_stream(_DT[table.dtype], _ptr(table), _ptr(ids), _ptr(out), rows, hidden, vocab,
+                                               self._err(), self._stream())
+            self._check(rc, "embedding_stream")
+            return out
         out = torch.empty(rows, hidden, dtype=table.dtype, device=table.device)
         rc = self.lib.pih_embedding(_DT[table.dtype], _ptr(table), _ptr(ids), _ptr(out), rows, hidden, vocab,
                                     self._err(), self._stream())
@@ -576,4 +588,157 @@ class CudaOps:
         rc = self.lib.pih_sample(_ptr(logits), rows, vocab, _ptr(fparams), _ptr(iparams), _ptr(out),
                                  self._err(), self._stream())
         self._check(rc, "sample")
+        return out
+
+    # -- a residual stream in 32-bit, mixers with state, attention over a latent, routed experts ------------------
+    def rmsnorm_stream(self, h: torch.Tensor, weight: torch.Tensor, eps: float, delta: Optional[torch.Tensor] = None,
+                       rows: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """RMS norm of a 32-bit stream: ``h += delta`` in 32-bit (stored back unless ``rows`` selects), then
+        ``h / sqrt(mean(h^2) + eps) * weight`` rounded to ``out_dtype``.  ``weight``: fp32, one number or one a column."""
+        width = h.shape[-1]
+        assert h.dtype == torch.float32 and h.is_contiguous() and weight.dtype == torch.float32
+        assert delta is None or (delta.is_contiguous() and delta.shape == h.shape)
+        n_out = h.numel() // width if rows is None else rows.shape[0]
+        out = torch.empty((n_out, width), dtype=out_dtype, device=h.device)
+        rc = self.lib.pih_rmsnorm_stream(_DT[delta.dtype] if delta is not None else 0, _DT[out_dtype], _ptr(h), _ptr(delta),
+                                         _ptr(weight), weight.numel(), _ptr(out), _ptr(rows), n_out, width, c_float(eps),
+                                         self._stream())
+        self._check(rc, "rmsnorm_stream")
+        return out
+
+    def linear_batched(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``out[t, b] = x[t, b] . w[b]^T``: x ``[T, B, K]`` (a view whose rows may be strided), w ``[B, N, K]``;
+        32-bit accumulation in ascending k; out ``[T, B, N]`` contiguous."""
+        T, B, K = x.shape
+        N = w.shape[1]
+        out_dtype = out_dtype or x.dtype
+        assert w.shape == (B, N, K) and w.is_contiguous() and x.dtype == w.dtype and x.stride(2) == 1
+        out = torch.empty(T, B, N, dtype=out_dtype, device=x.device)
+        if x.dtype == torch.bfloat16 and T > self.batched_library_min_rows:
+            # many rows in bf16: the library's batched product (32-bit accumulation)
+            torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1)) if out_dtype == x.dtype else \
+                out.copy_(torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32).transpose(0, 1))
+            return out
+        rc = self.lib.pih_gemm_simt_batched(_DT[x.dtype], _DT[out_dtype], _ptr(x), _ptr(w), _ptr(out), T, N, K,
+                                            c_ll(x.stride(0)), c_ll(K), c_ll(B * N), B, c_ll(x.stride(1)), c_ll(N * K),
+                                            c_ll(N), self._stream())
+        self._check(rc, "gemm_simt_batched")
+        return out
+
+    batched_library_min_rows = 1 << 30     # set lower to send bf16 batched products of many rows to the library
+
+    def causal_conv(self, x: torch.Tensor, w: torch.Tensor, *, step, state: torch.Tensor, state_offset: int,
+                    in_bias: Optional[torch.Tensor] = None, out_bias: Optional[torch.Tensor] = None,
+                    activation: Optional[str] = None) -> torch.Tensor:
+        """Short causal convolution per channel over each request's rows: x ``[T, C]`` (a view), w ``[C, taps]`` with
+        the last tap on the current row; ``in_bias`` is added to x first, ``out_bias`` to the sum; ``activation``
+        None or "silu".  The last ``taps - 1`` inputs of a request live in ``state[slot, state_offset:]`` as
+        ``[taps - 1, C]`` (fp32), are read as the rows before the step's and are replaced by the step's last ones."""
+        T, C = x.shape
+        taps = w.shape[1]
+        assert x.stride(1) == 1 and w.is_contiguous() and w.dtype == x.dtype and state.dtype == torch.float32
+        out = torch.empty(T, C, dtype=x.dtype, device=x.device)
+        rc = self.lib.pih_causal_conv(_DT[x.dtype], _ptr(x), c_ll(x.stride(0)), _ptr(w), _ptr(in_bias), _ptr(out_bias),
+                                      _ptr(out), c_ll(C), C, taps, {None: 0, "silu": 1}[activation], _ptr(state),
+                                      c_ll(state.stride(0)), c_ll(state_offset), _ptr(step.cu_q), _ptr(step.state_slots),
+                                      step.num_requests, self._stream())
+        self._check(rc, "causal_conv")
+        return out
+
+    def gated_delta_rule(self, qkv: torch.Tensor, ba: torch.Tensor, *, decay_log, decay_bias, state: torch.Tensor, step,
+                         heads: int, kv_heads: int, key_dim: int, value_dim: int, unit_eps: float,
+                         q_scale: float) -> torch.Tensor:
+        """The gated delta rule over the step's rows, request by request from each one's state slot
+        (``state[slot, :heads * key_dim * value_dim]`` is S).  qkv ``[T, 2 kv_heads key_dim + heads value_dim]``:
+        q heads, k heads, v heads after convolution and activation; ba ``[T, 2 heads]`` (a view): write-strength
+        logits, decay logits.  Returns the read-outs, fp32 ``[T, heads, value_dim]``."""
+        T = qkv.shape[0]
+        assert qkv.stride(1) == 1 and ba.stride(1) == 1 and ba.dtype == qkv.dtype
+        scratch = torch.empty(T * (2 * kv_heads * key_dim + 2 * heads), dtype=torch.float32, device=qkv.device)
+        out = torch.empty(T, heads, value_dim, dtype=torch.float32, device=qkv.device)
+        rc = self.lib.pih_gated_delta_rule(_DT[qkv.dtype], _ptr(qkv), c_ll(qkv.stride(0)), _ptr(ba), c_ll(ba.stride(0)),
+                                           _ptr(decay_log), _ptr(decay_bias), _ptr(scratch), _ptr(out), _ptr(state),
+                                           c_ll(state.stride(0)), _ptr(step.cu_q), _ptr(step.state_slots), T,
+                                           step.num_requests, heads, kv_heads, key_dim, value_dim, c_float(unit_eps),
+                                           c_float(q_scale), self._stream())
+        self._check(rc, "gated_delta_rule")
+        self.launches += 1                                     # two kernels
+        return out
+
+    def gated_rmsnorm(self, o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+        """``o / sqrt(mean(o^2) + eps) * weight * silu(gate)`` per (row, head): o fp32 ``[T, heads, vdim]``, gate
+        ``[T, heads * vdim]`` (a view), weight fp32 ``[vdim]``; returns ``[T, heads * vdim]`` in the gate's dtype."""
+        T, heads, vdim = o.shape
+        assert o.is_contiguous() and gate.stride(1) == 1
+        out = torch.empty(T, heads * vdim, dtype=gate.dtype, device=o.device)
+        rc = self.lib.pih_gated_rmsnorm(_DT[gate.dtype], _ptr(o), _ptr(gate), c_ll(gate.stride(0)), _ptr(weight), _ptr(out),
+                                        T, heads, vdim, c_float(eps), self._stream())
+        self._check(rc, "gated_rmsnorm")
+        return out
+
+    def rglru_scan(self, u: torch.Tensor, gates: torch.Tensor, y_pre: torch.Tensor, *, y_bias, r_bias, i_bias, lam,
+                   decay_scale: float, state: torch.Tensor, step, blocks: int) -> torch.Tensor:
+        """Real-gated linear recurrent unit over the step's rows from each request's state (``state[slot, :W]``):
+        ``a = exp(-decay_scale * sigmoid(gr + r_bias) * softplus(lam))``,
+        ``S <- a S + sqrt(1 - a^2) * sigmoid(gi + i_bias) * u``, out ``= S * gelu_tanh(y_pre + y_bias)``.
+        u ``[T, W]``; gates fp32 ``[T, blocks, 2 W / blocks]`` (a block's gr, then its gi); y_pre ``[T, W]`` (a view)."""
+        T, W = u.shape
+        assert u.stride(1) == 1 and y_pre.stride(1) == 1 and gates.is_contiguous() and gates.dtype == torch.float32
+        out = torch.empty(T, W, dtype=u.dtype, device=u.device)
+        rc = self.lib.pih_rglru_scan(_DT[u.dtype], _ptr(u), c_ll(u.stride(0)), _ptr(gates), _ptr(y_pre),
+                                     c_ll(y_pre.stride(0)), _ptr(y_bias), _ptr(r_bias), _ptr(i_bias), _ptr(lam),
+                                     c_float(decay_scale), _ptr(out), c_ll(W), _ptr(state), c_ll(state.stride(0)),
+                                     _ptr(step.cu_q), _ptr(step.state_slots), step.num_requests, W, blocks, self._stream())
+        self._check(rc, "rglru_scan")
+        return out
+
+    def latent_write(self, raw: torch.Tensor, weight: torch.Tensor, eps: float, cache: torch.Tensor,
+                     slot_mapping: torch.Tensor) -> None:
+        """``rmsnorm(raw) * weight`` of every row into its slot of the paged latent cache ``[pages, page_size, rank]``."""
+        T, rank = raw.shape
+        num_pages, page_size = cache.shape[0], cache.shape[1]
+        assert raw.stride(1) == 1 and cache.dtype == raw.dtype and cache.shape[2] == rank
+        rc = self.lib.pih_latent_write(_DT[raw.dtype], _ptr(raw), c_ll(raw.stride(0)), _ptr(weight), c_float(eps),
+                                       _ptr(cache), _ptr(slot_mapping), T, rank, page_size, num_pages, self._err(),
+                                       self._stream())
+        self._check(rc, "latent_write")
+
+    def latent_attention(self, q: torch.Tensor, *, gate: Optional[torch.Tensor], sink: Optional[torch.Tensor],
+                         cache: torch.Tensor, block_table: torch.Tensor, step, scale: float, window: int = 0) -> torch.Tensor:
+        """Causal attention of folded queries ``q [T, heads, rank]`` over the cached latents, which serve every head
+        as key and as value; ``sink`` (fp32 ``[heads]``) joins the softmax denominator; ``gate [T, heads]`` (a view of
+        logits) scales the output by its sigmoid.  Returns the weighted sums of latents ``[T, heads, rank]``."""
+        T, heads, rank = q.shape
+        num_pages, page_size = cache.shape[0], cache.shape[1]
+        assert q.is_contiguous() and (gate is None or gate.stride(1) == 1)
+        out = torch.empty_like(q)
+        rc = self.lib.pih_latent_attention_generic(
+            _DT[q.dtype], _ptr(q), _ptr(gate), c_ll(gate.stride(0) if gate is not None else 0), _ptr(sink), _ptr(cache),
+            _ptr(block_table), block_table.shape[1], _ptr(step.request_of_row), _ptr(step.positions), _ptr(out), T, heads,
+            rank, page_size, num_pages, c_float(scale), int(window), self._err(), self._stream())
+        self._check(rc, "latent_attention_generic")
+        return out
+
+    def moe_experts(self, x: torch.Tensor, logits: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
+                    w_down: torch.Tensor, top: int) -> torch.Tensor:
+        """Routed experts: per row the ``top`` largest of ``logits`` (fp32 ``[T, experts]``) choose, the softmax over
+        the chosen weighs; ``out = sum_k weight_k * W_down_e (silu(W_gate_e x) * (W_up_e x))``.  Weights are stacked
+        ``[experts, ff, hidden]`` / ``[experts, hidden, ff]``."""
+        T, hidden = x.shape
+        experts, ff = w_gate.shape[0], w_gate.shape[1]
+        assert logits.dtype == torch.float32 and logits.is_contiguous() and logits.shape == (T, experts)
+        assert x.stride(1) == 1 and w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous()
+        words = self.lib.pih_moe_route_words(T, experts, top)
+        ints = torch.zeros(int(words), dtype=torch.int32, device=x.device)
+        weight_of = torch.empty(T * top, dtype=torch.float32, device=x.device)
+        rc = self.lib.pih_moe_route(_ptr(logits), T, experts, top, _ptr(ints), _ptr(weight_of), self._stream())
+        self._check(rc, "moe_route")
+        act = torch.empty(T * top, ff, dtype=x.dtype, device=x.device)
+        y = torch.empty(T * top, hidden, dtype=torch.float32, device=x.device)
+        out = torch.empty(T, hidden, dtype=x.dtype, device=x.device)
+        rc = self.lib.pih_moe_experts(_DT[x.dtype], _ptr(x), c_ll(x.stride(0)), _ptr(w_gate), _ptr(w_up), _ptr(w_down),
+                                      _ptr(act), _ptr(y), _ptr(out), _ptr(ints), _ptr(weight_of), T, experts, top, hidden,
+                                      ff, self._stream())
+        self._check(rc, "moe_experts")
+        self.launches += 4                                     # three routing kernels, two products, the sum
         return out

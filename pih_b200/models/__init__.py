@@ -61,7 +61,8 @@ class CausalLM:
     @property
     def pad_safe(self) -> bool:
         """Whether a step may be padded to a larger shape: every mixer and feed-forward has to leave padding alone."""
-        return all(getattr(b.mixer, "pad_safe", False) and getattr(b.ffn, "pad_safe", False) for b in self.blocks)
+        return all(getattr(b.mixer, "pad_safe", False) and (b.ffn is None or getattr(b.ffn, "pad_safe", False))
+                   for b in self.blocks)
 
     # -- what the cache manager must provide, per schedule entry -------------
     def cache_needs(self) -> List[Optional[object]]:
@@ -79,7 +80,10 @@ class CausalLM:
         schedule entry i.  Returns fp32 logits ``[len(step.logit_rows), vocab]``
         or None when no logits are wanted."""
         ops = self.rt.ops
-        h = ops.embedding(self.embed, step.token_ids)
+        if self.spec.stream_dtype == "float32" and self.rt.dtype != torch.float32:
+            h = ops.embedding(self.embed, step.token_ids, out_dtype=torch.float32)      # the residual stream stays 32-bit
+        else:
+            h = ops.embedding(self.embed, step.token_ids)
         delta = None
         for i, entry in enumerate(self.spec.schedule):
             h, delta = self.blocks[entry.layer].forward(h, delta, step, caches[i])

@@ -7,6 +7,7 @@ sub-layer's output that is not yet added, so that the add fuses with the
 next norm wherever that norm lives (the next block's, or the model's final
 norm).  ``delta`` is None when the last sub-layer has added its output itself
 (for few rows the output projections add the residual in their epilogue).
+A layer whose spec has no feed-forward is ``h += mixer(norm_in(h))`` alone.
 """
 from __future__ import annotations
 
@@ -25,10 +26,11 @@ class PreNormBlock:
         n = spec.names
         for rel, info in part_class("norm", spec.norm_in.kind).expected_tensors(spec.norm_in).items():
             out[n["norm_in"] + rel] = info
-        for rel, info in part_class("norm", spec.norm_post.kind).expected_tensors(spec.norm_post).items():
-            out[n["norm_post"] + rel] = info
         out.update(part_class("mixer", spec.mixer.kind).expected_tensors(spec.mixer))
-        out.update(part_class("ffn", spec.ffn.kind).expected_tensors(spec.ffn))
+        if spec.ffn is not None:                   # a layer may have no feed-forward (and then no second norm)
+            for rel, info in part_class("norm", spec.norm_post.kind).expected_tensors(spec.norm_post).items():
+                out[n["norm_post"] + rel] = info
+            out.update(part_class("ffn", spec.ffn.kind).expected_tensors(spec.ffn))
         return out
 
     def __init__(self, spec, weights, rt: Runtime):
@@ -36,15 +38,17 @@ class PreNormBlock:
         self.rt = rt
         n = spec.names
         norm_in_cls = part_class("norm", spec.norm_in.kind)
-        norm_post_cls = part_class("norm", spec.norm_post.kind)
         mixer_cls = part_class("mixer", spec.mixer.kind)
-        ffn_cls = part_class("ffn", spec.ffn.kind)
         self.norm_in = norm_in_cls(
             spec.norm_in, _sub(weights, norm_in_cls.expected_tensors(spec.norm_in), n["norm_in"]), rt)
-        self.norm_post = norm_post_cls(
-            spec.norm_post, _sub(weights, norm_post_cls.expected_tensors(spec.norm_post), n["norm_post"]), rt)
         self.mixer = mixer_cls(spec.mixer, _sub(weights, mixer_cls.expected_tensors(spec.mixer)), rt)
-        self.ffn = ffn_cls(spec.ffn, _sub(weights, ffn_cls.expected_tensors(spec.ffn)), rt)
+        self.norm_post = self.ffn = None
+        if spec.ffn is not None:
+            norm_post_cls = part_class("norm", spec.norm_post.kind)
+            ffn_cls = part_class("ffn", spec.ffn.kind)
+            self.norm_post = norm_post_cls(
+                spec.norm_post, _sub(weights, norm_post_cls.expected_tensors(spec.norm_post), n["norm_post"]), rt)
+            self.ffn = ffn_cls(spec.ffn, _sub(weights, ffn_cls.expected_tensors(spec.ffn)), rt)
         self._native_ok = None             # decided at the first step
 
     def forward(self, h, delta, step, cache):
@@ -65,6 +69,8 @@ class PreNormBlock:
             h, a = self.mixer.forward_prenorm(h, delta, self.norm_in, step, cache)
         else:
             a = self.mixer.forward(self.norm_in.add_forward(h, delta), step, cache)
+        if self.ffn is None:
+            return h, a
         if fused_post and hasattr(self.ffn, "forward_prenorm"):
             return self.ffn.forward_prenorm(h, a, self.norm_post)
         return h, self.ffn.forward(self.norm_post.add_forward(h, a))

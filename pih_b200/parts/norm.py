@@ -11,6 +11,8 @@ the same values as the two separate kernels give.
 """
 from __future__ import annotations
 
+import torch
+
 from .registry import Runtime, TensorInfo, register_norm
 from ._bind import bind_vector
 
@@ -29,7 +31,37 @@ class RMSNorm:
         self.weight = bind_vector(weights["weight"], rt)
 
     def forward(self, x, rows=None):
-        return self.rt.ops.rmsnorm(x, self.weight, self.spec.eps, delta=None, rows=rows)
+        return self.add_forward(x, None, rows=rows)
 
     def add_forward(self, h, delta, rows=None):
+        if h.dtype != self.rt.dtype:
+            # a residual stream kept in 32-bit beside a 16-bit compute dtype: the sum stays 32-bit, the normed rows
+            # take the compute dtype
+            return self.rt.ops.rmsnorm_stream(h, self.weight.float(), self.spec.eps, delta=delta, rows=rows,
+                                              out_dtype=self.rt.dtype)
         return self.rt.ops.rmsnorm(h, self.weight, self.spec.eps, delta=delta, rows=rows)
+
+
+@register_norm("scalar_rmsnorm")
+class ScalarRMSNorm:
+    """``y = x / sqrt(mean(x^2) + eps) * g`` with ONE learned number ``g`` for all coordinates (a tensor without
+    axes, named by the block's norm prefix itself).  The stream ``h`` is 32-bit: ``add_forward`` sums ``h += delta``
+    in 32-bit and gives the normed rows in the compute dtype."""
+    fusable = False       # no product of the pack takes a one-number norm in its prologue
+
+    @classmethod
+    def expected_tensors(cls, spec):
+        return {"": TensorInfo((), "one_plus_normal")}
+
+    def __init__(self, spec, weights, rt: Runtime):
+        self.spec = spec
+        self.rt = rt
+        self.weight = weights[""].to(device=rt.device, dtype=torch.float32).reshape(1).contiguous()
+
+    def forward(self, x, rows=None):
+        return self.add_forward(x, None, rows=rows)
+
+    def add_forward(self, h, delta, rows=None):
+        if h.dtype != torch.float32:
+            raise TypeError("the one-number RMS norm reads a 32-bit stream")
+        return self.rt.ops.rmsnorm_stream(h, self.weight, self.spec.eps, delta=delta, rows=rows, out_dtype=self.rt.dtype)

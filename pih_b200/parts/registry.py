@@ -19,7 +19,7 @@ norm          ``forward(x) -> y`` and ``add_forward(h, delta) -> y`` which
 position      ``rotation_table() -> fp32 [max_positions, rotary_dim/2, 2]``
               (cos, sin) or None, and ``rotary_dim``; used by a mixer that
               rotates q and k.  Must be a pure function of the position.
-mixer         ``cache_need() -> PagedKVNeed | StateNeed | None`` and
+mixer         ``cache_need() -> PagedKVNeed | PagedVectorNeed | StateNeed | None`` and
               ``forward(x, step, cache) -> y`` with x, y ``[T, hidden]``;
               ``step`` is the engine's ``StepBatch`` (packed rows, request
               boundaries ``cu_q``, positions, state slots), ``cache`` the
@@ -39,7 +39,7 @@ import torch
 @dataclass(frozen=True)
 class TensorInfo:
     shape: Tuple[int, ...]
-    init: str = "normal"          # "normal" | "one_plus_normal" (random-weights mode)
+    init: str = "normal"          # "normal" | "one_plus_normal" | "conv" | "unit_normal" (random-weights mode)
 
 
 @dataclass(frozen=True)
@@ -47,6 +47,14 @@ class PagedKVNeed:
     """Keys and values per token.  ``window`` None: all keys are kept."""
     kv_heads: int
     head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class PagedVectorNeed:
+    """One vector of ``width`` numbers per token (a latent that keys and values are derived from), in pages
+    like keys and values: the group's tensor is ``[entries, pages, page_size, width]``."""
+    width: int
     window: Optional[int] = None
 
 

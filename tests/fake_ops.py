@@ -28,8 +28,8 @@ class FakeOps:
             self.clear_errors()
             raise RuntimeError(f"a kernel reported error code {code}")
 
-    def embedding(self, table, ids):
-        return table[ids.long()].clone()
+    def embedding(self, table, ids, out_dtype=None):
+        return table[ids.long()].to(out_dtype or table.dtype).clone()
 
     def rmsnorm(self, x, weight, eps, delta=None, rows=None):
         if rows is not None:
@@ -154,3 +154,139 @@ class FakeOps:
                                suppressed=[int(v) for v in iparams[i, 6:6 + nsup].tolist()])
             out.append(tok)
         return torch.tensor(out, dtype=torch.int32)
+
+    # -- a 32-bit residual stream, mixers with state, attention over a latent, routed experts ---------------------
+    def rmsnorm_stream(self, h, weight, eps, delta=None, rows=None, out_dtype=torch.bfloat16):
+        assert h.dtype == torch.float32
+        if rows is not None:
+            v = h[rows.long()]
+            if delta is not None:
+                v = v + delta[rows.long()].float()
+        else:
+            if delta is not None:
+                h += delta.float()
+            v = h
+        return (v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * weight).to(out_dtype)
+
+    def linear_batched(self, x, w, out_dtype=None):
+        return torch.einsum("tbk,bnk->tbn", x.float(), w.float()).to(out_dtype or x.dtype).contiguous()
+
+    @staticmethod
+    def _requests(step):
+        cu, slots = step.cu_q.tolist(), step.state_slots.tolist()
+        return [(cu[r], cu[r + 1], slots[r]) for r in range(len(slots)) if cu[r + 1] > cu[r] and slots[r] >= 0]
+
+    def causal_conv(self, x, w, *, step, state, state_offset, in_bias=None, out_bias=None, activation=None):
+        T, C = x.shape
+        taps = w.shape[1]
+        out = torch.zeros(T, C, dtype=x.dtype)
+        for lo, hi, slot in self._requests(step):
+            hist = state[slot, state_offset:state_offset + (taps - 1) * C].view(taps - 1, C)
+            xin = x[lo:hi].float() + (in_bias if in_bias is not None else 0.0)
+            seq = torch.cat([hist, xin], dim=0)
+            acc = torch.zeros(hi - lo, C)
+            for j in range(taps):
+                acc += seq[j:j + hi - lo] * w[:, j].float()[None, :]
+            if out_bias is not None:
+                acc += out_bias
+            if activation == "silu":
+                acc = acc * torch.sigmoid(acc)
+            out[lo:hi] = acc.to(x.dtype)
+            hist.copy_(seq[seq.shape[0] - (taps - 1):])
+        return out
+
+    def gated_delta_rule(self, qkv, ba, *, decay_log, decay_bias, state, step, heads, kv_heads, key_dim, value_dim,
+                         unit_eps, q_scale):
+        T = qkv.shape[0]
+        QK = kv_heads * key_dim
+        q = qkv[:, :QK].float().view(T, kv_heads, key_dim)
+        k = qkv[:, QK:2 * QK].float().view(T, kv_heads, key_dim)
+        v = qkv[:, 2 * QK:].float().view(T, heads, value_dim)
+        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + unit_eps) * q_scale
+        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+        beta = torch.sigmoid(ba[:, :heads].float())
+        decay = torch.exp(-torch.exp(decay_log) * torch.nn.functional.softplus(ba[:, heads:].float() + decay_bias))
+        out = torch.zeros(T, heads, value_dim)
+        per = heads // kv_heads
+        for lo, hi, slot in self._requests(step):
+            S = state[slot, :heads * key_dim * value_dim].view(heads, key_dim, value_dim)
+            for t in range(lo, hi):
+                for h in range(heads):
+                    kk, qq = k[t, h // per], q[t, h // per]
+                    S[h] *= decay[t, h]
+                    u = beta[t, h] * (v[t, h] - S[h].T @ kk)
+                    S[h] += torch.outer(kk, u)
+                    out[t, h] = S[h].T @ qq
+        return out
+
+    def gated_rmsnorm(self, o, gate, weight, eps):
+        T, heads, vdim = o.shape
+        g = gate.float().view(T, heads, vdim)
+        y = o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps) * weight * (g * torch.sigmoid(g))
+        return y.reshape(T, heads * vdim).to(gate.dtype)
+
+    def rglru_scan(self, u, gates, y_pre, *, y_bias, r_bias, i_bias, lam, decay_scale, state, step, blocks):
+        T, W = u.shape
+        bw = W // blocks
+        r = torch.sigmoid(gates[:, :, :bw].reshape(T, W) + r_bias)
+        i = torch.sigmoid(gates[:, :, bw:].reshape(T, W) + i_bias)
+        log_a = -decay_scale * r * torch.nn.functional.softplus(lam)
+        a = torch.exp(log_a)
+        mult = torch.sqrt(-torch.expm1(2 * log_a))
+        y = y_pre.float() + y_bias
+        y = 0.5 * y * (1 + torch.tanh(0.7978845608028654 * (y + 0.044715 * y ** 3)))
+        out = torch.zeros(T, W, dtype=u.dtype)
+        for lo, hi, slot in self._requests(step):
+            S = state[slot, :W]
+            for t in range(lo, hi):
+                S.copy_(a[t] * S + mult[t] * i[t] * u[t].float())
+                out[t] = (S * y[t]).to(u.dtype)
+        return out
+
+    def latent_write(self, raw, weight, eps, cache, slot_mapping):
+        v = raw.float()
+        c = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * weight
+        flat = cache.view(-1, cache.shape[-1])
+        for t, slot in enumerate(slot_mapping.tolist()):
+            if slot == -2:
+                continue
+            assert slot >= 0
+            flat[slot] = c[t].to(cache.dtype)
+
+    def latent_attention(self, q, *, gate, sink, cache, block_table, step, scale, window=0):
+        T, heads, rank = q.shape
+        page_size = cache.shape[1]
+        out = torch.zeros(T, heads, rank)
+        for t in range(T):
+            r = int(step.request_of_row[t])
+            if r < 0:
+                continue
+            p = int(step.positions[t])
+            js = torch.arange(max(0, p - window + 1) if window else 0, p + 1)
+            pages = block_table[r, (js // page_size).long()].long()
+            if not (pages >= 0).all():
+                self._report(2)
+                pages = pages.clamp(min=0)
+            C = cache[pages, (js % page_size).long()].float()                    # [n, rank]
+            s = (q[t].float() @ C.T) * scale                                     # [heads, n]
+            if sink is not None:
+                s = torch.cat([s, sink[:, None]], dim=1)
+            w = torch.softmax(s, dim=-1)[:, :C.shape[0]]
+            o = w @ C
+            if gate is not None:
+                o = o * torch.sigmoid(gate[t].float())[:, None]
+            out[t] = o
+        return out.to(q.dtype)
+
+    def moe_experts(self, x, logits, w_gate, w_up, w_down, top):
+        val, idx = torch.topk(logits, top, dim=-1)
+        wt = torch.softmax(val, dim=-1)
+        out = torch.zeros(x.shape, dtype=torch.float32)
+        xf = x.float()
+        for t in range(x.shape[0]):
+            for j in range(top):
+                e = int(idx[t, j])
+                g, u = (xf[t] @ w_gate[e].float().T).to(x.dtype).float(), (xf[t] @ w_up[e].float().T).to(x.dtype).float()
+                a = ((g * torch.sigmoid(g)) * u).to(x.dtype).float()
+                out[t] += wt[t, j] * (a @ w_down[e].float().T)
+        return out.to(x.dtype)
