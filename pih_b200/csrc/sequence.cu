@@ -123,7 +123,7 @@ causal_conv_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__
 
 // One block a row.  qk: [rows, ld] with q heads at column 0 and k heads at column kv_heads*dim (after convolution and
 // activation); ba: [rows, ldb] with the write-strength logits at column 0 and the decay logits at column ``heads``.
-// qn, kn: fp32 [rows, kv_heads, dim]; decay, beta: fp32 [rows, heads].
+// qn, kn: fp32 [rows, kv_heads, dim]; decay (as g - 1), beta: fp32 [rows, heads].
 template <typename T>
 __global__ void __launch_bounds__(128)
 delta_prepare_kernel(const T* __restrict__ qk, long long ld, const T* __restrict__ ba, long long ldb,
@@ -147,7 +147,8 @@ delta_prepare_kernel(const T* __restrict__ qk, long long ld, const T* __restrict
     const float b = to_float<T>(ba[static_cast<long long>(row) * ldb + h]);
     const float a = to_float<T>(ba[static_cast<long long>(row) * ldb + heads + h]);
     beta[static_cast<long long>(row) * heads + h] = sigmoid_f(b);
-    decay[static_cast<long long>(row) * heads + h] = expf(-expf(decay_log[h]) * softplus_f(a + decay_bias[h]));
+    // g - 1 rather than g: a decay next to 1 keeps its distance from 1 to full precision (see rglru_scan_kernel)
+    decay[static_cast<long long>(row) * heads + h] = expm1f(-expf(decay_log[h]) * softplus_f(a + decay_bias[h]));
   }
 }
 
@@ -195,7 +196,7 @@ __global__ void delta_recurrence_kernel(const float* __restrict__ qn, const floa
 #pragma unroll
       for (int e = 0; e < kMaxPer; ++e) nxt[e] = e < per ? fetch(t + 1, e) : 0.0f;
     }
-    const float g = decay[static_cast<long long>(t) * heads + h];
+    const float gm1 = decay[static_cast<long long>(t) * heads + h];        // g - 1; g x is formed as x + (g - 1) x
     const float b = beta[static_cast<long long>(t) * heads + h];
     const float vj = live ? to_float<T>(v[static_cast<long long>(t) * ldv + static_cast<long long>(h) * vdim + col]) : 0.0f;
     const float* k = cur;
@@ -209,19 +210,20 @@ __global__ void delta_recurrence_kernel(const float* __restrict__ qn, const floa
       a3 = fmaf(S[(i + 3) * cols + j], k[i + 3], a3);
     }
     for (; i < dim; ++i) a0 = fmaf(S[i * cols + j], k[i], a0);
-    const float u = b * (vj - g * ((a0 + a1) + (a2 + a3)));
+    const float dot = (a0 + a1) + (a2 + a3);
+    const float u = b * (vj - fmaf(gm1, dot, dot));
     float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
     i = 0;
     for (; i + 4 <= dim; i += 4) {
-      const float s0 = fmaf(k[i + 0], u, g * S[(i + 0) * cols + j]);
-      const float s1 = fmaf(k[i + 1], u, g * S[(i + 1) * cols + j]);
-      const float s2 = fmaf(k[i + 2], u, g * S[(i + 2) * cols + j]);
-      const float s3 = fmaf(k[i + 3], u, g * S[(i + 3) * cols + j]);
+      const float s0 = fmaf(k[i + 0], u, fmaf(gm1, S[(i + 0) * cols + j], S[(i + 0) * cols + j]));
+      const float s1 = fmaf(k[i + 1], u, fmaf(gm1, S[(i + 1) * cols + j], S[(i + 1) * cols + j]));
+      const float s2 = fmaf(k[i + 2], u, fmaf(gm1, S[(i + 2) * cols + j], S[(i + 2) * cols + j]));
+      const float s3 = fmaf(k[i + 3], u, fmaf(gm1, S[(i + 3) * cols + j], S[(i + 3) * cols + j]));
       S[(i + 0) * cols + j] = s0; S[(i + 1) * cols + j] = s1; S[(i + 2) * cols + j] = s2; S[(i + 3) * cols + j] = s3;
       o0 = fmaf(s0, q[i + 0], o0); o1 = fmaf(s1, q[i + 1], o1); o2 = fmaf(s2, q[i + 2], o2); o3 = fmaf(s3, q[i + 3], o3);
     }
     for (; i < dim; ++i) {
-      const float s0 = fmaf(k[i], u, g * S[i * cols + j]);
+      const float s0 = fmaf(k[i], u, fmaf(gm1, S[i * cols + j], S[i * cols + j]));
       S[i * cols + j] = s0;
       o0 = fmaf(s0, q[i], o0);
     }
@@ -281,9 +283,12 @@ rglru_scan_kernel(const T* __restrict__ u, long long ldu, const float* __restric
     const float rg = sigmoid_f(g[o] + rb);
     const float ig = sigmoid_f(g[bw + o] + ib);
     const float log_a = -rate * rg;
-    const float a = expf(log_a);
-    const float mult = sqrtf(-expm1f(2.0f * log_a));            // sqrt(1 - a^2) without the cancellation near a = 1
-    S = fmaf(a, S, mult * (ig * to_float<T>(u[static_cast<long long>(t) * ldu + c])));
+    // a = exp(log_a) lies next to 1 for a channel that remembers long, where 32-bit numbers are 6e-8 apart: a rounded
+    // there would be off by a few percent of 1 - a, and a thousand steps would multiply that up.  So a - 1 and
+    // 1 - a^2 come from expm1, and a S is formed as S + (a - 1) S.
+    const float am1 = expm1f(log_a);
+    const float mult = sqrtf(-expm1f(2.0f * log_a));
+    S = fmaf(am1, S, fmaf(mult, ig * to_float<T>(u[static_cast<long long>(t) * ldu + c]), S));
     const float y = gelu_tanh_f(to_float<T>(y_pre[static_cast<long long>(t) * ldy + c]) + yb);
     out[static_cast<long long>(t) * ldo + c] = from_float<T>(S * y);
   }
