@@ -292,6 +292,114 @@ def e2e_run(config, model_dir_weights, batch: int, steps: int, warmup: int):
             "ms_per_step": dt / steps * 1e3}
 
 
+# -- the Rigotar design beside the dense decoder at equal width ---------------------------------------------------
+def _rigotar_config(width: int, layers: int, kinds=("rglru", "latent_attention", "delta", "latent_attention"), moe=True,
+                    vocab: int = 32768):
+    """Layer sizes that resemble a real model's at this width: 128-wide heads, a latent of a quarter of the width,
+    sixteen experts of which two are used, with as many active feed-forward weights as the dense model's."""
+    heads = width // 128
+    mixers = {"delta": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "conv": 4},
+              "rglru": {"width": width, "blocks": heads, "conv": 4},
+              "latent_attention": {"heads": heads, "dim": 128, "vdim": 128, "kv_rank": width // 4, "scale": 128 ** -0.5}}
+    mlp = {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": 3 * width // 2}} if moe else None
+    return {"architecture": "Rigotar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "layers": [{"type": kinds[i % len(kinds)], "mixer": mixers[kinds[i % len(kinds)]], "mlp": mlp}
+                       for i in range(layers)]}
+
+
+def _dense_config(width: int, layers: int, vocab: int = 32768):
+    return dict(QWEN3_0_6B, hidden_size=width, intermediate_size=3 * width, num_hidden_layers=layers,
+                num_attention_heads=width // 128 * 2, num_key_value_heads=width // 128, head_dim=128, vocab_size=vocab,
+                tie_word_embeddings=False, bos_token_id=1, eos_token_id=2)
+
+
+def _build(raw):
+    import torch
+    from pih_b200.config import config_from_dict
+    from pih_b200.kernels import get_ops
+    from pih_b200.models import CausalLM, expected_tensors
+    from pih_b200.parts import Runtime
+    from pih_b200.weights import random_tensors
+    spec = config_from_dict(raw).model_spec()
+    dev = torch.device("cuda:0")
+    weights = random_tensors(expected_tensors(spec), seed=2, sigma=0.02, dtype=torch.bfloat16)
+    return CausalLM(spec, weights, Runtime(dev, torch.bfloat16, get_ops(dev)))
+
+
+def _timed_steps(model, batch: int, context: int, prompt: int, steps: int):
+    """(ms of one prompt of ``prompt`` tokens in one step, ms of a decode step of ``batch`` requests holding ``context``
+    tokens each), device-timed, medians; the requests' contexts are run through the model so that states and caches
+    hold what the model wrote."""
+    import torch
+    from pih_b200.engine import StepEntry
+    from pih_b200.engine.factory import runner_for
+    rt = model.rt
+    g = torch.Generator().manual_seed(5)
+    cache, runner = runner_for(model, page_size=PAGE, max_cache_tokens=batch * (context + 2 * steps + 64) + prompt + 64,
+                               max_requests=batch + 1, cuda_graphs=True, capture_decode_after=2)
+
+    def timed(fn):
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b)
+
+    toks = torch.randint(0, model.spec.vocab, (prompt,), generator=g).tolist()
+    pre = []
+    for i in range(6):
+        pre.append(timed(lambda: runner.step([StepEntry("p", toks, [prompt - 1])])))
+        runner.finish("p")
+    for r in range(batch):
+        runner.step([StepEntry(r, torch.randint(0, model.spec.vocab, (context,), generator=g).tolist(), [])])
+    tokens = torch.randint(0, model.spec.vocab, (batch,), generator=g).tolist()
+
+    def decode():
+        for _ in range(steps):
+            rt.ops.argmax(runner.step([StepEntry(r, [tokens[r]], [0]) for r in range(batch)]))
+
+    decode()                                               # (captures the decode shape)
+    dec = sorted(timed(decode) / steps for _ in range(3))[1]
+    rt.ops.check_errors()
+    for r in range(batch):
+        runner.finish(r)
+    return sorted(pre[2:])[len(pre[2:]) // 2], dec
+
+
+def design_run(args) -> int:
+    """``--design rigotar``: prompt and decode throughput of the Rigotar design at two widths with layer sizes that
+    resemble a real model's (random weights, bf16), beside the dense decoder at the same width, depth and number of
+    active feed-forward weights; and every mixer alone (four layers of it, no feed-forward) beside the dense model's
+    attention-only time, so that each kind of layer can be read off.  One JSON line."""
+    import torch
+    rows = []
+    batch, context, prompt, steps = args.batch, CONTEXT, PREFILL_TOKENS, max(8, args.steps // 4)
+    with ClockSampler() as clocks:
+        for width in (1024, 2048):
+            cases = [("rigotar", _rigotar_config(width, 8)), ("dense", _dense_config(width, 8))]
+            if width == 1024:
+                cases += [(f"rigotar {k} x4, no feed-forward", _rigotar_config(width, 4, kinds=(k,), moe=False))
+                          for k in ("rglru", "latent_attention", "delta")]
+                cases += [("rigotar rglru x4 with experts", _rigotar_config(width, 4, kinds=("rglru",)))]
+            for name, raw in cases:
+                model = _build(raw)
+                pre_ms, dec_ms = _timed_steps(model, batch, context, prompt, steps)
+                rows.append({"model": name, "width": width, "layers": len(raw.get("layers", [])) or raw["num_hidden_layers"],
+                             "prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(prompt / pre_ms * 1e3),
+                             "decode_ms": round(dec_ms, 4), "decode_tok_s": round(batch / dec_ms * 1e3)})
+                del model
+                gc.collect()
+                torch.cuda.empty_cache()
+        clock_summary = clocks.summary()
+    print(json.dumps({"metric": "prompt and decode tok/s of the Rigotar design beside the dense decoder", "dtype": "bf16",
+                      "data": "synthetic", "n_gpus": 1, "config": {"prompt_tokens": prompt, "decode_batch": batch,
+                                                                   "context": context, "page_size": PAGE},
+                      "rows": rows, "clocks": clock_summary}))
+    return 0
+
+
 def reference_arm():
     print(json.dumps({"impl": "reference", "unavailable":
                       "pip installs only pih_client, an HTTP client; the engine is a C++20/CUDA worker (CMake) whose "
@@ -311,6 +419,8 @@ def main() -> int:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
+    ap.add_argument("--design", default=None, choices=["rigotar"],
+                    help="instead of the recorded workload: this design's prompt and decode throughput beside the dense decoder's")
     ap.add_argument("--plain-launches", action="store_true",
                     help="launch kernels fully serialised instead of with programmatic dependent launch")
     args = ap.parse_args()
@@ -321,6 +431,9 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+
+    if args.design == "rigotar":
+        return design_run(args)
 
     import torch
     hbm_gbs, bf16_tflops, peak_src = peaks()

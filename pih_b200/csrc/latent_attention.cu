@@ -11,7 +11,8 @@
 // row's result does not depend on how its prompt was cut or batched.
 //
 //   latent_write              c = rmsnorm(raw latent) * w  ->  the paged cache [pages, page_size, rank]
-//   latent_attention_generic  one warp a (row, head), any rank up to 512, float or bf16 storage
+//   latent_attention_generic  one warp a (row, head), keys in order: any rank up to 512; the 32-bit path
+//   latent_attention_split    a block a (row, part of its keys, 8 heads) and a merge: the serving path
 #include "common.cuh"
 
 namespace pih {
@@ -111,6 +112,154 @@ latent_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ g
   }
 }
 
+
+// The same attention for the serving dtype, cut over keys.  Block (row, split of the row's keys, group of 8 heads):
+// 8 warps, a head each; a tile of 32 cached latents is brought into shared memory ONCE for the 8 heads.  Scores: a
+// lane a key (the folded query is read as a broadcast, the latent row with a padded pitch, conflict-free); weights
+// and running sums in 32-bit; the weighted sum of latents: a lane a column.  A split leaves (maximum, sum, weighted
+// sum) per head; latent_merge folds the splits in order, starting from the sink, and applies 1 / sum and the gate.
+// rank a multiple of 4.
+template <typename T, int kPerLane>
+__global__ void __launch_bounds__(256)
+latent_attention_split_kernel(const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ block_table,
+                              int table_width, const int* __restrict__ request_of_row, const int* __restrict__ positions,
+                              float* __restrict__ partial, int heads, int rank, int page_size, int num_pages, float scale,
+                              int window, int splits, uint32_t* err) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ long long src_row[32];
+  constexpr int kUnit = 4 / sizeof(T);                           // elements in a 32-bit unit
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int row = blockIdx.x, split = blockIdx.y, h0 = blockIdx.z * 8;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, h = h0 + warp;
+  const int req = request_of_row[row];
+  if (req < 0) return;                                           // a row of padding
+  float* qs = reinterpret_cast<float*>(smem_raw);                // [8][rank]
+  T* tile = reinterpret_cast<T*>(qs + 8 * rank);                 // [32][pitch]
+  const int pitch = rank + (sizeof(T) == 2 ? 2 : 1);             // an odd number of 32-bit words
+  const int pos = positions[row];
+  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  const int chunk = (((pos - first + 1) + splits - 1) / splits + 31) / 32 * 32;
+  const int k0 = first + split * chunk, k1 = min(pos + 1, k0 + chunk);
+  for (int i = tid; i < 8 * rank; i += 256) {
+    const int hh = h0 + i / rank;
+    qs[i] = hh < heads ? to_float<T>(q[(static_cast<long long>(row) * heads + hh) * rank + i % rank]) : 0.0f;
+  }
+  float m = -INFINITY, l = 0.0f, acc[kPerLane];
+#pragma unroll
+  for (int e = 0; e < kPerLane; ++e) acc[e] = 0.0f;
+  const int* table = block_table + static_cast<long long>(req) * table_width;
+  const int units = rank / kUnit;
+  for (int t0 = k0; t0 < k1; t0 += 32) {
+    __syncthreads();                                             // the tile before this one has been used
+    if (tid < 32) {
+      const int key = t0 + tid;
+      long long src = -1;
+      if (key < k1) {
+        const int pi = key / page_size;
+        const int page = pi < table_width ? table[pi] : -1;
+        if (page < 0 || page >= num_pages) publish_error(err, kRowWithoutPage);
+        else src = (static_cast<long long>(page) * page_size + (key - pi * page_size)) * rank;
+      }
+      src_row[tid] = src;
+    }
+    __syncthreads();
+    for (int i = tid; i < 32 * units; i += 256) {
+      const int j = i / units, un = i - j * units;
+      const long long src = src_row[j];
+      uint32_t word = 0u;
+      if (src >= 0) word = *reinterpret_cast<const uint32_t*>(cache + src + un * kUnit);
+      *reinterpret_cast<uint32_t*>(tile + j * pitch + un * kUnit) = word;
+    }
+    __syncthreads();
+    if (h < heads) {
+      const T* cj = tile + lane * pitch;
+      const float* qh = qs + warp * rank;
+      float s0 = 0.0f, s1 = 0.0f;
+      for (int r = 0; r < rank; r += 4) {
+        const float4 qv = *reinterpret_cast<const float4*>(qh + r);
+        s0 = fmaf(qv.x, to_float<T>(cj[r + 0]), s0);
+        s1 = fmaf(qv.y, to_float<T>(cj[r + 1]), s1);
+        s0 = fmaf(qv.z, to_float<T>(cj[r + 2]), s0);
+        s1 = fmaf(qv.w, to_float<T>(cj[r + 3]), s1);
+      }
+      const bool valid = t0 + lane < k1 && src_row[lane] >= 0;
+      const float sc = valid ? (s0 + s1) * scale : -INFINITY;
+      const float m_new = fmaxf(m, warp_max(sc));
+      if (m_new > -INFINITY) {
+        const float corr = expf(m - m_new);
+        const float p = valid ? expf(sc - m_new) : 0.0f;
+        l = fmaf(l, corr, warp_sum(p));
+#pragma unroll
+        for (int e = 0; e < kPerLane; ++e) acc[e] *= corr;
+        for (int j = 0; j < 32; ++j) {
+          const float pj = __shfl_sync(0xffffffffu, p, j);
+          const T* c = tile + j * pitch;
+#pragma unroll
+          for (int e = 0; e < kPerLane; ++e) {
+            const int i = lane + 32 * e;
+            if (e * 32 < rank && i < rank) acc[e] = fmaf(pj, to_float<T>(c[i]), acc[e]);
+          }
+        }
+        m = m_new;
+      }
+    }
+  }
+  if (h < heads) {
+    float* dst = partial + ((static_cast<long long>(row) * heads + h) * splits + split) * (rank + 2);
+    if (lane == 0) { dst[0] = m; dst[1] = l; }
+#pragma unroll
+    for (int e = 0; e < kPerLane; ++e) {
+      const int i = lane + 32 * e;
+      if (i < rank) dst[2 + i] = acc[e];
+    }
+  }
+}
+
+// One warp a (row, head): the splits in order, from the sink.
+template <typename T>
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(const float* __restrict__ partial, const T* __restrict__ gate, long long ldg,
+                    const float* __restrict__ sink, const int* __restrict__ request_of_row, T* __restrict__ out, int rows,
+                    int heads, int rank, int splits, uint32_t* err) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= static_cast<long long>(rows) * heads) return;
+  const int lane = threadIdx.x & 31;
+  const int row = static_cast<int>(item / heads), h = static_cast<int>(item % heads);
+  if (request_of_row[row] < 0) return;
+  float m = sink != nullptr ? sink[h] : -INFINITY;
+  float l = sink != nullptr ? 1.0f : 0.0f;
+  const float* base = partial + item * splits * (rank + 2);
+  // first the maximum and the sum over the splits, then the columns with each split's factor
+  float m_all = m;
+  for (int s = 0; s < splits; ++s)
+    if (base[s * (rank + 2) + 1] > 0.0f) m_all = fmaxf(m_all, base[s * (rank + 2)]);
+  l = l * expf(m - m_all);
+  for (int s = 0; s < splits; ++s) {
+    const float ls = base[s * (rank + 2) + 1];
+    if (ls > 0.0f) l = fmaf(ls, expf(base[s * (rank + 2)] - m_all), l);
+  }
+  if (!(l > 0.0f) || !isfinite(l)) {
+    if (lane == 0) publish_error(err, kAttentionDenominator);
+    l = 1.0f;
+  }
+  float factor = 1.0f / l;
+  if (gate != nullptr) {
+    const float z = to_float<T>(gate[static_cast<long long>(row) * ldg + h]);
+    factor *= 1.0f / (1.0f + expf(-z));
+  }
+  for (int i = lane; i < rank; i += 32) {
+    float a = 0.0f;
+    for (int s = 0; s < splits; ++s) {
+      const float* ps = base + s * (rank + 2);
+      if (ps[1] > 0.0f) a = fmaf(ps[2 + i], expf(ps[0] - m_all), a);
+    }
+    out[item * rank + i] = from_float<T>(a * factor);
+  }
+}
+
 }  // namespace pih
 
 using namespace pih;
@@ -162,6 +311,58 @@ extern "C" int pih_latent_attention_generic(int dtype, const void* q, const void
   else return PIH_ERR_BAD_ARGUMENT;
 #undef PIH_LA
 #undef PIH_LA1
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+// Splits of a row's keys for a step of ``rows`` rows: enough blocks to fill the GPU, a function of the step's shape only.
+extern "C" int pih_latent_attention_splits(int rows, int heads) {
+  const int groups = (heads + 7) / 8;
+  const int per_row = (2 * 148) / (rows * groups > 0 ? rows * groups : 1);
+  return per_row < 1 ? 1 : (per_row > 32 ? 32 : per_row);
+}
+
+// partial: fp32 scratch, rows * heads * splits * (rank + 2)
+extern "C" int pih_latent_attention_split(int dtype, const void* q, const void* gate, long long ldg, const void* sink,
+                                          const void* cache, const void* block_table, int table_width,
+                                          const void* request_of_row, const void* positions, void* partial, void* out,
+                                          int rows, int heads, int rank, int page_size, int num_pages, float scale,
+                                          int window, int splits, void* err, void* stream) {
+  if (rows <= 0) return 0;
+  if (rank > 32 * kLatentPerLane || rank % 4 || splits < 1 || rows > 65535 * 32) return PIH_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int esize = dtype == PIH_F32 ? 4 : 2;
+  const size_t smem = 8 * static_cast<size_t>(rank) * 4 + 32 * static_cast<size_t>(rank + (esize == 2 ? 2 : 1)) * esize;
+  dim3 grid(rows, splits, (heads + 7) / 8);
+  const long long items = static_cast<long long>(rows) * heads;
+#define PIH_LS1(T, NE)                                                                                                 \
+  do {                                                                                                                 \
+    if (smem > 48 * 1024)                                                                                              \
+      cudaFuncSetAttribute(latent_attention_split_kernel<T, NE>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
+                           static_cast<int>(smem));                                                                    \
+    launch_kernel(latent_attention_split_kernel<T, NE>, grid, dim3(256), smem, s, static_cast<const T*>(q),            \
+                  static_cast<const T*>(cache), static_cast<const int*>(block_table), table_width,                     \
+                  static_cast<const int*>(request_of_row), static_cast<const int*>(positions),                         \
+                  static_cast<float*>(partial), heads, rank, page_size, num_pages, scale, window, splits,              \
+                  static_cast<uint32_t*>(err));                                                                        \
+  } while (0)
+#define PIH_LS(T)                                                                                                      \
+  do {                                                                                                                 \
+    if (rank <= 64) PIH_LS1(T, 2);                                                                                     \
+    else if (rank <= 128) PIH_LS1(T, 4);                                                                               \
+    else if (rank <= 256) PIH_LS1(T, 8);                                                                               \
+    else PIH_LS1(T, 16);                                                                                               \
+    PIH_LAUNCH_CHECK();                                                                                                \
+    launch_kernel(latent_merge_kernel<T>, dim3(static_cast<unsigned>((items + 3) / 4)), dim3(128), 0, s,               \
+                  static_cast<const float*>(partial), static_cast<const T*>(gate), ldg, static_cast<const float*>(sink), \
+                  static_cast<const int*>(request_of_row), static_cast<T*>(out), rows, heads, rank, splits,            \
+                  static_cast<uint32_t*>(err));                                                                        \
+  } while (0)
+  if (dtype == PIH_F32) PIH_LS(float);
+  else if (dtype == PIH_BF16) PIH_LS(bf16);
+  else return PIH_ERR_BAD_ARGUMENT;
+#undef PIH_LS
+#undef PIH_LS1
   PIH_LAUNCH_CHECK();
   return 0;
 }

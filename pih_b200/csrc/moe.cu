@@ -99,12 +99,13 @@ __global__ void moe_scatter_kernel(const int* __restrict__ expert_of, const int*
 }
 
 // The grouped product.  kGated: two weight matrices per expert and silu(a) * b in the epilogue.  A's rows are
-// gathered through ``row_of`` when it is given (else row = position).  W: [experts, N, K] contiguous.
+// gathered through ``row_of`` when it is given (else row = position).  Expert e's matrices [N, K] start
+// ``e * expert_stride`` elements behind W0 and W1.
 template <typename TA, typename TC, bool kGated>
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ row_of, const TA* __restrict__ W0,
-                   const TA* __restrict__ W1, TC* __restrict__ C, long long ldc, const int* __restrict__ plan,
-                   int experts, int N, int K) {
+                   const TA* __restrict__ W1, long long expert_stride, TC* __restrict__ C, long long ldc,
+                   const int* __restrict__ plan, int experts, int N, int K) {
   constexpr int BM = kMoeTile, BN = 64, BK = 16, TM = 4, TN = 4;
   wait_for_prior_kernels();
   launch_dependents();
@@ -139,8 +140,8 @@ moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restric
   __syncthreads();
   const int tx = tid % (BN / TN), ty = tid / (BN / TN);
   const int n0 = blockIdx.x * BN;
-  const TA* w0 = W0 + static_cast<long long>(e) * N * K;
-  const TA* w1 = kGated ? W1 + static_cast<long long>(e) * N * K : nullptr;
+  const TA* w0 = W0 + e * expert_stride;
+  const TA* w1 = kGated ? W1 + e * expert_stride : nullptr;
   float acc[kGated ? 2 : 1][TM][TN];
 #pragma unroll
   for (int g = 0; g < (kGated ? 2 : 1); ++g)
@@ -212,8 +213,69 @@ moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restric
   }
 }
 
-template <typename T>
-__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ pos_of,
+
+// Few rows (a decode step): every (row, choice) slot on its own, a warp an output column, the expert's weight rows
+// read with 16-byte loads, four columns in flight a warp.  x row of slot s: s / row_div.  kGated: act[s][n] =
+// silu(x . W0_e[n]) * (x . W1_e[n]); else out[out_index[s]][n] = x . W0_e[n] (32-bit).  K a multiple of 8 (4 in 32-bit).
+template <typename T, typename TC, bool kGated>
+__global__ void __launch_bounds__(256)
+moe_gemv_kernel(const T* __restrict__ x, long long ldx, int row_div, const int* __restrict__ expert_of,
+                const T* __restrict__ W0, const T* __restrict__ W1, long long expert_stride, TC* __restrict__ out,
+                long long ldo, const int* __restrict__ out_index, int N, int K) {
+  constexpr int kVec = 16 / sizeof(T), kCols = 4;
+  extern __shared__ float xs[];
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int slot = blockIdx.x;
+  const int e = expert_of[slot];
+  const T* xr = x + static_cast<long long>(slot / row_div) * ldx;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float<T>(xr[k]);
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n0 = (blockIdx.y * (blockDim.x >> 5) + warp) * kCols;
+  if (n0 >= N) return;
+  const T* w0 = W0 + e * expert_stride;
+  const T* w1 = kGated ? W1 + e * expert_stride : nullptr;
+  float a0[kCols], a1[kCols];
+#pragma unroll
+  for (int c = 0; c < kCols; ++c) a0[c] = a1[c] = 0.0f;
+  for (int k = lane * kVec; k < K; k += 32 * kVec) {
+    float xv[kVec];
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) xv[i] = xs[k + i];
+#pragma unroll
+    for (int c = 0; c < kCols; ++c) {
+      const int n = min(n0 + c, N - 1);
+      __align__(16) T wv[kVec];
+      *reinterpret_cast<uint4*>(wv) = *reinterpret_cast<const uint4*>(w0 + static_cast<long long>(n) * K + k);
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) a0[c] = fmaf(to_float<T>(wv[i]), xv[i], a0[c]);
+      if (kGated) {
+        *reinterpret_cast<uint4*>(wv) = *reinterpret_cast<const uint4*>(w1 + static_cast<long long>(n) * K + k);
+#pragma unroll
+        for (int i = 0; i < kVec; ++i) a1[c] = fmaf(to_float<T>(wv[i]), xv[i], a1[c]);
+      }
+    }
+  }
+  const long long orow = out_index != nullptr ? out_index[slot] : slot;
+#pragma unroll
+  for (int c = 0; c < kCols; ++c) {
+    float g = warp_sum(a0[c]);
+    float u = kGated ? warp_sum(a1[c]) : 0.0f;
+    if (lane == 0 && n0 + c < N) {
+      if (kGated) {
+        g = round_to<T>(g);
+        u = round_to<T>(u);
+        out[orow * ldo + n0 + c] = from_float<TC>((g / (1.0f + expf(-g))) * u);
+      } else {
+        out[orow * ldo + n0 + c] = from_float<TC>(g);
+      }
+    }
+  }
+}
+
+template <typename T, typename TY>
+__global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ pos_of,
                                    const float* __restrict__ weight_of, T* __restrict__ out, int rows, int hidden, int top) {
   wait_for_prior_kernels();
   launch_dependents();
@@ -222,7 +284,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     float acc = 0.0f;
     for (int k = 0; k < top; ++k) {
       const long long i = static_cast<long long>(row) * top + k;
-      acc = fmaf(weight_of[i], y[static_cast<long long>(pos_of[i]) * hidden + c], acc);
+      acc = fmaf(weight_of[i], to_float<TY>(y[static_cast<long long>(pos_of[i]) * hidden + c]), acc);
     }
     out[static_cast<long long>(row) * hidden + c] = from_float<T>(acc);
   }
@@ -262,11 +324,13 @@ extern "C" int pih_moe_route(const void* logits, int rows, int experts, int top,
   return 0;
 }
 
-// x [rows, lda]; w_gate, w_up [experts, ff, hidden]; w_down [experts, hidden, ff]; act [slots, ff] (storage type);
-// y fp32 [slots, hidden]; out [rows, hidden] (storage type).
-extern "C" int pih_moe_experts(int dtype, const void* x, long long lda, const void* w_gate, const void* w_up,
-                               const void* w_down, void* act, void* y, void* out, const void* ints, const void* weight_of,
-                               int rows, int experts, int top, int hidden, int ff, void* stream) {
+// x [rows, lda]; w_gate_up [experts, 2 ff, hidden]: an expert's gate rows, then its up rows; w_down [experts, hidden, ff];
+// act [slots, ff] (storage type); y fp32 [slots, hidden]; out [rows, hidden] (storage type).  few_rows: every slot on
+// its own (the weight rows streamed with 16-byte loads) instead of the grouped product; needs hidden and ff to be
+// multiples of 8 (bf16) or 4 (32-bit) and hidden, ff <= 12288.
+extern "C" int pih_moe_experts(int dtype, const void* x, long long lda, const void* w_gate_up, const void* w_down, void* act,
+                               void* y, void* out, const void* ints, const void* weight_of, int rows, int experts, int top,
+                               int hidden, int ff, int few_rows, void* stream) {
   if (rows <= 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const long long slots = static_cast<long long>(rows) * top;
@@ -276,18 +340,36 @@ extern "C" int pih_moe_experts(int dtype, const void* x, long long lda, const vo
   const int* plan = row_of + slots + experts;
   const unsigned tiles = static_cast<unsigned>((slots + kMoeTile - 1) / kMoeTile + experts);
   if (tiles > 65535) return PIH_ERR_UNSUPPORTED;
+  const long long gu_stride = 2LL * ff * hidden, down_stride = static_cast<long long>(hidden) * ff;
+  if (few_rows) {
+    const int vec = dtype == PIH_F32 ? 4 : 8;
+    if (hidden % vec || ff % vec || hidden > 12288 || ff > 12288 || slots > 65535) return PIH_ERR_UNSUPPORTED;
+  }
 #define PIH_MOE(T)                                                                                                     \
   do {                                                                                                                 \
-    launch_kernel(moe_grouped_kernel<T, T, true>, dim3((ff + 63) / 64, tiles), dim3(256), 0, s,                        \
-                  static_cast<const T*>(x), lda, row_of, static_cast<const T*>(w_gate), static_cast<const T*>(w_up),   \
-                  static_cast<T*>(act), static_cast<long long>(ff), plan, experts, ff, hidden);                        \
+    const T* wgu = static_cast<const T*>(w_gate_up);                                                                   \
+    if (few_rows) {                                                                                                    \
+      launch_kernel(moe_gemv_kernel<T, T, true>, dim3(static_cast<unsigned>(slots), (ff + 31) / 32), dim3(256),        \
+                    hidden * sizeof(float), s, static_cast<const T*>(x), lda, top, expert_of, wgu,                     \
+                    wgu + static_cast<long long>(ff) * hidden, gu_stride, static_cast<T*>(act),                        \
+                    static_cast<long long>(ff), static_cast<const int*>(nullptr), ff, hidden);                         \
+      PIH_LAUNCH_CHECK();                                                                                              \
+      launch_kernel(moe_gemv_kernel<T, float, false>, dim3(static_cast<unsigned>(slots), (hidden + 31) / 32),          \
+                    dim3(256), ff * sizeof(float), s, static_cast<const T*>(act), static_cast<long long>(ff), 1,       \
+                    expert_of, static_cast<const T*>(w_down), static_cast<const T*>(nullptr), down_stride,             \
+                    static_cast<float*>(y), static_cast<long long>(hidden), pos_of, hidden, ff);                       \
+    } else {                                                                                                           \
+      launch_kernel(moe_grouped_kernel<T, T, true>, dim3((ff + 63) / 64, tiles), dim3(256), 0, s,                      \
+                    static_cast<const T*>(x), lda, row_of, wgu, wgu + static_cast<long long>(ff) * hidden, gu_stride,  \
+                    static_cast<T*>(act), static_cast<long long>(ff), plan, experts, ff, hidden);                      \
+      PIH_LAUNCH_CHECK();                                                                                              \
+      launch_kernel(moe_grouped_kernel<T, float, false>, dim3((hidden + 63) / 64, tiles), dim3(256), 0, s,             \
+                    static_cast<const T*>(act), static_cast<long long>(ff), static_cast<const int*>(nullptr),          \
+                    static_cast<const T*>(w_down), static_cast<const T*>(nullptr), down_stride,                        \
+                    static_cast<float*>(y), static_cast<long long>(hidden), plan, experts, hidden, ff);                \
+    }                                                                                                                  \
     PIH_LAUNCH_CHECK();                                                                                                \
-    launch_kernel(moe_grouped_kernel<T, float, false>, dim3((hidden + 63) / 64, tiles), dim3(256), 0, s,               \
-                  static_cast<const T*>(act), static_cast<long long>(ff), static_cast<const int*>(nullptr),            \
-                  static_cast<const T*>(w_down), static_cast<const T*>(nullptr), static_cast<float*>(y),               \
-                  static_cast<long long>(hidden), plan, experts, hidden, ff);                                          \
-    PIH_LAUNCH_CHECK();                                                                                                \
-    launch_kernel(moe_combine_kernel<T>, dim3(rows), dim3(hidden >= 256 ? 256 : 128), 0, s,                            \
+    launch_kernel(moe_combine_kernel<T, float>, dim3(rows), dim3(hidden >= 256 ? 256 : 128), 0, s,                     \
                   static_cast<const float*>(y), pos_of, static_cast<const float*>(weight_of), static_cast<T*>(out),    \
                   rows, hidden, top);                                                                                  \
   } while (0)
@@ -295,6 +377,19 @@ extern "C" int pih_moe_experts(int dtype, const void* x, long long lda, const vo
   else if (dtype == PIH_BF16) PIH_MOE(bf16);
   else return PIH_ERR_BAD_ARGUMENT;
 #undef PIH_MOE
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+// out[row] = sum_k weight_of[row][k] * y[pos_of[row][k]] for y in bf16 (the output of a library's grouped product)
+extern "C" int pih_moe_combine_bf16(const void* y, const void* ints, const void* weight_of, void* out, int rows, int top,
+                                    int hidden, void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int* pos_of = static_cast<const int*>(ints) + 2LL * rows * top;
+  launch_kernel(moe_combine_kernel<bf16, bf16>, dim3(rows), dim3(hidden >= 256 ? 256 : 128), 0, s,
+                static_cast<const bf16*>(y), pos_of, static_cast<const float*>(weight_of), static_cast<bf16*>(out), rows,
+                hidden, top);
   PIH_LAUNCH_CHECK();
   return 0;
 }

@@ -7,7 +7,7 @@
 //   delta_prepare         unit-norm q and k per head, decay and write strength per head (32-bit)
 //   delta_recurrence      gated delta rule: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q
 //   gated_rmsnorm         per-head RMS norm of the read-out, times a weight, times silu(gate)
-//   rglru_scan            real-gated linear recurrent unit: S <- a S + sqrt(1 - a^2) (i u), out = S * gelu(y)
+//   rglru_gates, _chain   real-gated linear recurrent unit: S <- a S + sqrt(1 - a^2) (i u), out = S * gelu(y)
 //
 // A step's rows are packed: request r owns rows cu_q[r] .. cu_q[r+1]-1 in the order of their positions, and
 // state_slots[r] is its slot in the state tensor (fp32, ``state_stride`` numbers a slot).  Kernels that carry state
@@ -233,6 +233,99 @@ __global__ void delta_recurrence_kernel(const float* __restrict__ qn, const floa
     for (int i = 0; i < dim; ++i) Sg[static_cast<long long>(i) * vdim + col] = S[i * cols + j];
 }
 
+// The same recurrence with S in registers, for the key sizes that have an instance.  Block (request, head, 32 value
+// columns) of 128 threads: thread (column c = tid / 4, part p = tid % 4) holds rows p * kDim / 4 ... of column c, so the
+// four parts of a column sit in neighbouring lanes and meet through two shuffles.  k and q of a token are staged in
+// shared memory (two buffers, one barrier a token); the next token's k, q, v, decay and write strength are fetched
+// while this token is computed.  The order of the additions is fixed by the kernel, not by the step's make-up.
+template <typename T, int kDim>
+__global__ void __launch_bounds__(128)
+delta_recurrence_reg_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const T* __restrict__ v,
+                            long long ldv, const float* __restrict__ decay, const float* __restrict__ beta,
+                            float* __restrict__ out, float* __restrict__ state, long long state_stride,
+                            const int* __restrict__ cu_q, const int* __restrict__ state_slots, int heads, int kv_heads,
+                            int vdim) {
+  constexpr int kRows = kDim / 4;                 // rows of S a thread holds
+  constexpr int kFetch = (2 * kDim + 127) / 128;  // numbers of k|q a thread fetches
+  __shared__ __align__(16) float kq[2][2 * kDim];
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int tid = threadIdx.x, part = tid & 3, col = blockIdx.z * 32 + (tid >> 2);
+  const int lo = cu_q[r], hi = cu_q[r + 1];
+  const int slot = state_slots[r];
+  if (hi <= lo || slot < 0) return;
+  const int kh = h / (heads / kv_heads);
+  const bool live = col < vdim;
+  float* Sg = state + slot * state_stride + (static_cast<long long>(h) * kDim + part * kRows) * vdim;
+  float S[kRows];
+#pragma unroll
+  for (int i = 0; i < kRows; ++i) S[i] = live ? Sg[static_cast<long long>(i) * vdim + col] : 0.0f;
+  auto fetch = [&](int t, int e) -> float {
+    const int idx = tid + e * 128;
+    if (idx >= 2 * kDim) return 0.0f;
+    const float* src = idx < kDim ? kn : qn;
+    return src[(static_cast<long long>(t) * kv_heads + kh) * kDim + (idx < kDim ? idx : idx - kDim)];
+  };
+  float nxt[kFetch];
+#pragma unroll
+  for (int e = 0; e < kFetch; ++e) nxt[e] = fetch(lo, e);
+  float gm1_n = decay[static_cast<long long>(lo) * heads + h], b_n = beta[static_cast<long long>(lo) * heads + h];
+  float v_n = live ? to_float<T>(v[static_cast<long long>(lo) * ldv + static_cast<long long>(h) * vdim + col]) : 0.0f;
+  for (int t = lo; t < hi; ++t) {
+    float* cur = kq[t & 1];
+#pragma unroll
+    for (int e = 0; e < kFetch; ++e)
+      if (tid + e * 128 < 2 * kDim) cur[tid + e * 128] = nxt[e];
+    const float gm1 = gm1_n, b = b_n, vj = v_n;
+    __syncthreads();
+    if (t + 1 < hi) {
+#pragma unroll
+      for (int e = 0; e < kFetch; ++e) nxt[e] = fetch(t + 1, e);
+      gm1_n = decay[static_cast<long long>(t + 1) * heads + h];
+      b_n = beta[static_cast<long long>(t + 1) * heads + h];
+      v_n = live ? to_float<T>(v[static_cast<long long>(t + 1) * ldv + static_cast<long long>(h) * vdim + col]) : 0.0f;
+    }
+    const float* k = cur + part * kRows;
+    const float* q = cur + kDim + part * kRows;
+    float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kRows; i += 4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(k + i);
+      a0 = fmaf(S[i + 0], k4.x, a0);
+      a1 = fmaf(S[i + 1], k4.y, a1);
+      a0 = fmaf(S[i + 2], k4.z, a0);
+      a1 = fmaf(S[i + 3], k4.w, a1);
+    }
+    float dot = a0 + a1;
+    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+    const float u = b * (vj - fmaf(gm1, dot, dot));
+    float o0 = 0.0f, o1 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kRows; i += 4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(k + i);
+      const float4 q4 = *reinterpret_cast<const float4*>(q + i);
+      S[i + 0] = fmaf(k4.x, u, fmaf(gm1, S[i + 0], S[i + 0]));
+      S[i + 1] = fmaf(k4.y, u, fmaf(gm1, S[i + 1], S[i + 1]));
+      S[i + 2] = fmaf(k4.z, u, fmaf(gm1, S[i + 2], S[i + 2]));
+      S[i + 3] = fmaf(k4.w, u, fmaf(gm1, S[i + 3], S[i + 3]));
+      o0 = fmaf(S[i + 0], q4.x, o0);
+      o1 = fmaf(S[i + 1], q4.y, o1);
+      o0 = fmaf(S[i + 2], q4.z, o0);
+      o1 = fmaf(S[i + 3], q4.w, o1);
+    }
+    float o = o0 + o1;
+    o += __shfl_xor_sync(0xffffffffu, o, 1);
+    o += __shfl_xor_sync(0xffffffffu, o, 2);
+    if (live && part == 0) out[(static_cast<long long>(t) * heads + h) * vdim + col] = o;
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) Sg[static_cast<long long>(i) * vdim + col] = S[i];
+  }
+}
+
 // One warp a (row, head): o fp32 [rows, heads, vdim]; gate [rows, ldg] with head h at column h * vdim.
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -258,15 +351,41 @@ gated_rmsnorm_kernel(const float* __restrict__ o, const T* __restrict__ gate, lo
   }
 }
 
-// Thread a (request, channel).  gates: fp32 [rows, blocks, 2 * bw]: block b's decay-gate logits, then its input-gate
-// logits (without their biases).  y_pre [rows, ldy]: the other branch before its bias and GELU.
+// The unit in two kernels.  rglru_gates (a thread a (row, channel), every row at once): from the gate logits
+// (gates: fp32 [rows, blocks, 2 * bw]: block b's decay-gate logits, then its input-gate logits, without their biases),
+// the convolution's output u and the other branch y_pre [rows, ldy] before its bias and GELU, the three numbers that
+// the recurrence needs of a token: coef[row][c] = (a - 1, sqrt(1 - a^2) * i * u, gelu(y), 0).  rglru_chain (a thread a
+// (request, channel)): S <- S + (a - 1) S + b, out = S * y over the request's rows in order, eight tokens' numbers in
+// flight ahead of the chain.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rglru_gates_kernel(const T* __restrict__ u, long long ldu, const float* __restrict__ gates, const T* __restrict__ y_pre,
+                   long long ldy, const float* __restrict__ y_bias, const float* __restrict__ r_bias,
+                   const float* __restrict__ i_bias, const float* __restrict__ lam, float decay_scale,
+                   float4* __restrict__ coef, int rows, int width, int blocks) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(rows) * width) return;
+  const int t = static_cast<int>(idx / width), c = static_cast<int>(idx % width);
+  const int bw = width / blocks, b = c / bw, o = c % bw;
+  const float* g = gates + (static_cast<long long>(t) * blocks + b) * (2 * bw);
+  const float rg = sigmoid_f(g[o] + r_bias[c]);
+  const float ig = sigmoid_f(g[bw + o] + i_bias[c]);
+  const float log_a = -(decay_scale * softplus_f(lam[c])) * rg;
+  // a = exp(log_a) lies next to 1 for a channel that remembers long, where 32-bit numbers are 6e-8 apart: a rounded
+  // there would be off by a few percent of 1 - a, and a thousand steps would multiply that up.  So a - 1 and
+  // 1 - a^2 come from expm1, and a S is formed as S + (a - 1) S.
+  const float am1 = expm1f(log_a);
+  const float mult = sqrtf(-expm1f(2.0f * log_a));
+  const float y = gelu_tanh_f(to_float<T>(y_pre[static_cast<long long>(t) * ldy + c]) + y_bias[c]);
+  coef[idx] = make_float4(am1, mult, ig * to_float<T>(u[static_cast<long long>(t) * ldu + c]), y);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
-rglru_scan_kernel(const T* __restrict__ u, long long ldu, const float* __restrict__ gates, const T* __restrict__ y_pre,
-                  long long ldy, const float* __restrict__ y_bias, const float* __restrict__ r_bias,
-                  const float* __restrict__ i_bias, const float* __restrict__ lam, float decay_scale, T* __restrict__ out,
-                  long long ldo, float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
-                  const int* __restrict__ state_slots, int width, int blocks) {
+rglru_chain_kernel(const float4* __restrict__ coef, T* __restrict__ out, long long ldo, float* __restrict__ state,
+                   long long state_stride, const int* __restrict__ cu_q, const int* __restrict__ state_slots, int width) {
   wait_for_prior_kernels();
   launch_dependents();
   const int r = blockIdx.x;
@@ -274,23 +393,20 @@ rglru_scan_kernel(const T* __restrict__ u, long long ldu, const float* __restric
   const int lo = cu_q[r], hi = cu_q[r + 1];
   const int slot = state_slots[r];
   if (hi <= lo || slot < 0 || c >= width) return;
-  const int bw = width / blocks, b = c / bw, o = c % bw;
   float S = state[slot * state_stride + c];
-  const float rate = decay_scale * softplus_f(lam[c]);
-  const float rb = r_bias[c], ib = i_bias[c], yb = y_bias[c];
-  for (int t = lo; t < hi; ++t) {
-    const float* g = gates + (static_cast<long long>(t) * blocks + b) * (2 * bw);
-    const float rg = sigmoid_f(g[o] + rb);
-    const float ig = sigmoid_f(g[bw + o] + ib);
-    const float log_a = -rate * rg;
-    // a = exp(log_a) lies next to 1 for a channel that remembers long, where 32-bit numbers are 6e-8 apart: a rounded
-    // there would be off by a few percent of 1 - a, and a thousand steps would multiply that up.  So a - 1 and
-    // 1 - a^2 come from expm1, and a S is formed as S + (a - 1) S.
-    const float am1 = expm1f(log_a);
-    const float mult = sqrtf(-expm1f(2.0f * log_a));
-    S = fmaf(am1, S, fmaf(mult, ig * to_float<T>(u[static_cast<long long>(t) * ldu + c]), S));
-    const float y = gelu_tanh_f(to_float<T>(y_pre[static_cast<long long>(t) * ldy + c]) + yb);
-    out[static_cast<long long>(t) * ldo + c] = from_float<T>(S * y);
+  constexpr int kAhead = 8;
+  for (int t0 = lo; t0 < hi; t0 += kAhead) {
+    float4 f[kAhead];
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i)
+      f[i] = t0 + i < hi ? coef[static_cast<long long>(t0 + i) * width + c] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i) {
+      if (t0 + i < hi) {
+        S = fmaf(f[i].x, S, fmaf(f[i].y, f[i].z, S));
+        out[static_cast<long long>(t0 + i) * ldo + c] = from_float<T>(S * f[i].w);
+      }
+    }
   }
   state[slot * state_stride + c] = S;
 }
@@ -382,24 +498,38 @@ extern "C" int pih_gated_delta_rule(int dtype, const void* qkv, long long ld, co
   dim3 grid(requests, heads, (vdim + cols - 1) / cols);
   if (grid.y > 65535 || grid.z > 65535) return PIH_ERR_UNSUPPORTED;
   const long long qk_size = static_cast<long long>(kv_heads) * dim;
+#define PIH_DELTA_REG(T, D)                                                                                            \
+  launch_kernel(delta_recurrence_reg_kernel<T, D>, dim3(requests, heads, (vdim + 31) / 32), dim3(128), 0, s,           \
+                static_cast<const float*>(qn), static_cast<const float*>(kn), static_cast<const T*>(qkv) + 2 * qk_size, \
+                ld, static_cast<const float*>(decay), static_cast<const float*>(beta), static_cast<float*>(out),       \
+                static_cast<float*>(state), state_stride, static_cast<const int*>(cu_q),                               \
+                static_cast<const int*>(state_slots), heads, kv_heads, vdim)
 #define PIH_DELTA(T)                                                                                                   \
   do {                                                                                                                 \
     launch_kernel(delta_prepare_kernel<T>, dim3(rows), dim3(128), 0, s, static_cast<const T*>(qkv), ld,                \
                   static_cast<const T*>(ba), ldb, static_cast<const float*>(decay_log),                                \
                   static_cast<const float*>(decay_bias), qn, kn, decay, beta, heads, kv_heads, dim, unit_eps, q_scale); \
     PIH_LAUNCH_CHECK();                                                                                                \
-    if (smem > 48 * 1024)                                                                                              \
-      cudaFuncSetAttribute(delta_recurrence_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
-    launch_kernel(delta_recurrence_kernel<T>, grid, dim3(cols), smem, s, static_cast<const float*>(qn),                \
-                  static_cast<const float*>(kn), static_cast<const T*>(qkv) + 2 * qk_size, ld,                         \
-                  static_cast<const float*>(decay), static_cast<const float*>(beta), static_cast<float*>(out),         \
-                  static_cast<float*>(state), state_stride, static_cast<const int*>(cu_q),                             \
-                  static_cast<const int*>(state_slots), heads, kv_heads, dim, vdim);                                   \
+    if (dim == 16) PIH_DELTA_REG(T, 16);                                                                               \
+    else if (dim == 32) PIH_DELTA_REG(T, 32);                                                                          \
+    else if (dim == 64) PIH_DELTA_REG(T, 64);                                                                          \
+    else if (dim == 128) PIH_DELTA_REG(T, 128);                                                                        \
+    else if (dim == 256) PIH_DELTA_REG(T, 256);                                                                        \
+    else {                                                                                                             \
+      if (smem > 48 * 1024)                                                                                            \
+        cudaFuncSetAttribute(delta_recurrence_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \
+      launch_kernel(delta_recurrence_kernel<T>, grid, dim3(cols), smem, s, static_cast<const float*>(qn),              \
+                    static_cast<const float*>(kn), static_cast<const T*>(qkv) + 2 * qk_size, ld,                       \
+                    static_cast<const float*>(decay), static_cast<const float*>(beta), static_cast<float*>(out),       \
+                    static_cast<float*>(state), state_stride, static_cast<const int*>(cu_q),                           \
+                    static_cast<const int*>(state_slots), heads, kv_heads, dim, vdim);                                 \
+    }                                                                                                                  \
   } while (0)
   if (dtype == PIH_F32) PIH_DELTA(float);
   else if (dtype == PIH_BF16) PIH_DELTA(bf16);
   else return PIH_ERR_BAD_ARGUMENT;
 #undef PIH_DELTA
+#undef PIH_DELTA_REG
   PIH_LAUNCH_CHECK();
   return 0;
 }
@@ -421,22 +551,30 @@ extern "C" int pih_gated_rmsnorm(int dtype, const void* o, const void* gate, lon
   return 0;
 }
 
+// coef: scratch, 4 * rows * width floats (16-byte aligned)
 extern "C" int pih_rglru_scan(int dtype, const void* u, long long ldu, const void* gates, const void* y_pre, long long ldy,
                               const void* y_bias, const void* r_bias, const void* i_bias, const void* lam,
-                              float decay_scale, void* out, long long ldo, void* state, long long state_stride,
-                              const void* cu_q, const void* state_slots, int requests, int width, int blocks,
+                              float decay_scale, void* coef, void* out, long long ldo, void* state, long long state_stride,
+                              const void* cu_q, const void* state_slots, int rows, int requests, int width, int blocks,
                               void* stream) {
-  if (requests <= 0 || width <= 0) return 0;
+  if (requests <= 0 || width <= 0 || rows <= 0) return 0;
   if (blocks < 1 || width % blocks) return PIH_ERR_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 grid(requests, (width + 127) / 128);
-  if (grid.y > 65535) return PIH_ERR_UNSUPPORTED;
+  const long long items = static_cast<long long>(rows) * width;
+  if (grid.y > 65535 || (items + 255) / 256 > 2147483647LL) return PIH_ERR_UNSUPPORTED;
 #define PIH_SCAN(T)                                                                                                    \
-  launch_kernel(rglru_scan_kernel<T>, grid, dim3(128), 0, s, static_cast<const T*>(u), ldu,                            \
-                static_cast<const float*>(gates), static_cast<const T*>(y_pre), ldy, static_cast<const float*>(y_bias), \
-                static_cast<const float*>(r_bias), static_cast<const float*>(i_bias), static_cast<const float*>(lam),  \
-                decay_scale, static_cast<T*>(out), ldo, static_cast<float*>(state), state_stride,                      \
-                static_cast<const int*>(cu_q), static_cast<const int*>(state_slots), width, blocks)
+  do {                                                                                                                 \
+    launch_kernel(rglru_gates_kernel<T>, dim3(static_cast<unsigned>((items + 255) / 256)), dim3(256), 0, s,            \
+                  static_cast<const T*>(u), ldu, static_cast<const float*>(gates), static_cast<const T*>(y_pre), ldy,  \
+                  static_cast<const float*>(y_bias), static_cast<const float*>(r_bias),                                \
+                  static_cast<const float*>(i_bias), static_cast<const float*>(lam), decay_scale,                      \
+                  static_cast<float4*>(coef), rows, width, blocks);                                                    \
+    PIH_LAUNCH_CHECK();                                                                                                \
+    launch_kernel(rglru_chain_kernel<T>, grid, dim3(128), 0, s, static_cast<const float4*>(coef), static_cast<T*>(out), \
+                  ldo, static_cast<float*>(state), state_stride, static_cast<const int*>(cu_q),                        \
+                  static_cast<const int*>(state_slots), width);                                                        \
+  } while (0)
   if (dtype == PIH_F32) PIH_SCAN(float);
   else if (dtype == PIH_BF16) PIH_SCAN(bf16);
   else return PIH_ERR_BAD_ARGUMENT;

@@ -107,7 +107,7 @@ class CudaOps:
                      "pih_qk_attention_fused", "pih_gemm_tcgen05_pair", "pih_set_attention_side_by_side", "pih_set_skinny_rule",
                      "pih_gemm_simt_batched", "pih_embedding_stream", "pih_rmsnorm_stream", "pih_causal_conv",
                      "pih_gated_delta_rule", "pih_gated_rmsnorm", "pih_rglru_scan", "pih_latent_write",
-                     "pih_latent_attention_generic", "pih_moe_route", "pih_moe_experts"):
+                     "pih_latent_attention_generic", "pih_moe_route", "pih_moe_experts", "pih_moe_combine_bf16", "pih_latent_attention_split", "pih_latent_attention_splits"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
         lib.pih_top_logprobs_scratch_words.restype = c_ll
@@ -533,6 +533,14 @@ class CudaOps:
         self._check(rc, "paged_attention_generic")
         return out
 
+    def gather_rows(self, x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        """``x[rows]`` for contiguous x ``[n, width]`` and int32 ``rows``."""
+        assert x.is_contiguous() and rows.dtype == torch.int32
+        out = torch.empty(rows.shape[0], x.shape[1], dtype=x.dtype, device=x.device)
+        rc = self.lib.pih_gather_rows(_DT[x.dtype], _ptr(x), _ptr(rows), _ptr(out), rows.shape[0], x.shape[1], self._stream())
+        self._check(rc, "gather_rows")
+        return out
+
     def silu_mul(self, gate_up: torch.Tensor, interleave: Optional[int] = None) -> torch.Tensor:
         """``silu(g) * u``; the columns of ``gate_up`` come in blocks of ``interleave`` gate columns
         followed by their up columns (default: all gates, then all ups)."""
@@ -625,6 +633,7 @@ class CudaOps:
         self._check(rc, "gemm_simt_batched")
         return out
 
+    latent_split = True                    # bf16 attention over a latent: keys cut into parts (False: the in-order kernel)
     batched_library_min_rows = 1 << 30     # set lower to send bf16 batched products of many rows to the library
 
     def causal_conv(self, x: torch.Tensor, w: torch.Tensor, *, step, state: torch.Tensor, state_offset: int,
@@ -685,11 +694,14 @@ class CudaOps:
         T, W = u.shape
         assert u.stride(1) == 1 and y_pre.stride(1) == 1 and gates.is_contiguous() and gates.dtype == torch.float32
         out = torch.empty(T, W, dtype=u.dtype, device=u.device)
+        coef = torch.empty(T, W, 4, dtype=torch.float32, device=u.device)     # per (row, channel): a - 1, the input's two factors, gelu(y)
         rc = self.lib.pih_rglru_scan(_DT[u.dtype], _ptr(u), c_ll(u.stride(0)), _ptr(gates), _ptr(y_pre),
                                      c_ll(y_pre.stride(0)), _ptr(y_bias), _ptr(r_bias), _ptr(i_bias), _ptr(lam),
-                                     c_float(decay_scale), _ptr(out), c_ll(W), _ptr(state), c_ll(state.stride(0)),
-                                     _ptr(step.cu_q), _ptr(step.state_slots), step.num_requests, W, blocks, self._stream())
+                                     c_float(decay_scale), _ptr(coef), _ptr(out), c_ll(W), _ptr(state), c_ll(state.stride(0)),
+                                     _ptr(step.cu_q), _ptr(step.state_slots), T, step.num_requests, W, blocks,
+                                     self._stream())
         self._check(rc, "rglru_scan")
+        self.launches += 1                                     # two kernels
         return out
 
     def latent_write(self, raw: torch.Tensor, weight: torch.Tensor, eps: float, cache: torch.Tensor,
@@ -712,6 +724,21 @@ class CudaOps:
         num_pages, page_size = cache.shape[0], cache.shape[1]
         assert q.is_contiguous() and (gate is None or gate.stride(1) == 1)
         out = torch.empty_like(q)
+        if q.dtype == torch.bfloat16 and self.latent_split and rank % 4 == 0:
+            # the serving path: a row's keys are cut into parts that run side by side (as many as fill the GPU for this
+            # number of rows) and a tile of latents is fetched once for 8 heads.  The 32-bit path keeps the kernel that
+            # visits a row's keys in order, whose result does not depend on the step's make-up by a single bit.
+            splits = self.lib.pih_latent_attention_splits(T, heads)
+            partial = torch.empty(T * heads * splits * (rank + 2), dtype=torch.float32, device=q.device)
+            rc = self.lib.pih_latent_attention_split(
+                _DT[q.dtype], _ptr(q), _ptr(gate), c_ll(gate.stride(0) if gate is not None else 0), _ptr(sink), _ptr(cache),
+                _ptr(block_table), block_table.shape[1], _ptr(step.request_of_row), _ptr(step.positions), _ptr(partial),
+                _ptr(out), T, heads, rank, page_size, num_pages, c_float(scale), int(window), splits, self._err(),
+                self._stream())
+            if rc != -2:
+                self._check(rc, "latent_attention_split")
+                self.launches += 1
+                return out
         rc = self.lib.pih_latent_attention_generic(
             _DT[q.dtype], _ptr(q), _ptr(gate), c_ll(gate.stride(0) if gate is not None else 0), _ptr(sink), _ptr(cache),
             _ptr(block_table), block_table.shape[1], _ptr(step.request_of_row), _ptr(step.positions), _ptr(out), T, heads,
@@ -719,26 +746,55 @@ class CudaOps:
         self._check(rc, "latent_attention_generic")
         return out
 
-    def moe_experts(self, x: torch.Tensor, logits: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
-                    w_down: torch.Tensor, top: int) -> torch.Tensor:
+    moe_few_slots = 64            # bf16 steps of at most this many (row, choice) slots stream the chosen experts' rows
+    moe_library_min_slots = 65    # ... and from this many on the experts' products are the library's grouped product
+
+    def moe_experts(self, x: torch.Tensor, logits: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+                    top: int) -> torch.Tensor:
         """Routed experts: per row the ``top`` largest of ``logits`` (fp32 ``[T, experts]``) choose, the softmax over
-        the chosen weighs; ``out = sum_k weight_k * W_down_e (silu(W_gate_e x) * (W_up_e x))``.  Weights are stacked
-        ``[experts, ff, hidden]`` / ``[experts, hidden, ff]``."""
+        the chosen weighs; ``out = sum_k weight_k * W_down_e (silu(W_gate_e x) * (W_up_e x))``.  ``w_gate_up``
+        ``[experts, 2 ff, hidden]`` holds an expert's gate rows and then its up rows, ``w_down`` ``[experts, hidden, ff]``.
+
+        Routing, grouping by expert and the weighted sum are the pack's kernels.  The experts' products: in 32-bit
+        the pack's grouped FMA product (an order of additions fixed by the row); in bf16 a step of few rows streams
+        each chosen expert's rows once (a warp a column), and a step of many rows runs the library's grouped product
+        (``torch._grouped_mm``: tensor cores, the groups' boundaries read on the device) where the pack's dense
+        products of many rows are the library's too."""
         T, hidden = x.shape
-        experts, ff = w_gate.shape[0], w_gate.shape[1]
+        experts, ff = w_gate_up.shape[0], w_gate_up.shape[1] // 2
         assert logits.dtype == torch.float32 and logits.is_contiguous() and logits.shape == (T, experts)
-        assert x.stride(1) == 1 and w_gate.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous()
+        assert x.stride(1) == 1 and w_gate_up.is_contiguous() and w_down.is_contiguous()
+        slots = T * top
         words = self.lib.pih_moe_route_words(T, experts, top)
         ints = torch.zeros(int(words), dtype=torch.int32, device=x.device)
-        weight_of = torch.empty(T * top, dtype=torch.float32, device=x.device)
+        weight_of = torch.empty(slots, dtype=torch.float32, device=x.device)
         rc = self.lib.pih_moe_route(_ptr(logits), T, experts, top, _ptr(ints), _ptr(weight_of), self._stream())
         self._check(rc, "moe_route")
-        act = torch.empty(T * top, ff, dtype=x.dtype, device=x.device)
-        y = torch.empty(T * top, hidden, dtype=torch.float32, device=x.device)
+        self.launches += 2
         out = torch.empty(T, hidden, dtype=x.dtype, device=x.device)
-        rc = self.lib.pih_moe_experts(_DT[x.dtype], _ptr(x), c_ll(x.stride(0)), _ptr(w_gate), _ptr(w_up), _ptr(w_down),
-                                      _ptr(act), _ptr(y), _ptr(out), _ptr(ints), _ptr(weight_of), T, experts, top, hidden,
-                                      ff, self._stream())
+        bf16 = x.dtype == torch.bfloat16
+        if (bf16 and slots >= self.moe_library_min_slots and hidden % 8 == 0 and ff % 8 == 0
+                and hasattr(torch, "_grouped_mm")):
+            row_of = ints[3 * slots:4 * slots]
+            ends = ints[4 * slots + experts + 1:4 * slots + 2 * experts + 1]          # where each expert's rows end
+            xs = self.gather_rows(x, row_of) if x.is_contiguous() else x.index_select(0, row_of)
+            gate_up = torch._grouped_mm(xs, w_gate_up.transpose(1, 2), offs=ends)     # [slots, 2 ff]
+            act = self.silu_mul(gate_up)
+            y = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends)             # [slots, hidden]
+            rc = self.lib.pih_moe_combine_bf16(_ptr(y), _ptr(ints), _ptr(weight_of), _ptr(out), T, top, hidden,
+                                               self._stream())
+            self._check(rc, "moe_combine")
+            return out
+        act = torch.empty(slots, ff, dtype=x.dtype, device=x.device)
+        y = torch.empty(slots, hidden, dtype=torch.float32, device=x.device)
+        few = 1 if (bf16 and slots <= self.moe_few_slots) else 0
+        rc = self.lib.pih_moe_experts(_DT[x.dtype], _ptr(x), c_ll(x.stride(0)), _ptr(w_gate_up), _ptr(w_down), _ptr(act),
+                                      _ptr(y), _ptr(out), _ptr(ints), _ptr(weight_of), T, experts, top, hidden, ff, few,
+                                      self._stream())
+        if rc == -2 and few:
+            rc = self.lib.pih_moe_experts(_DT[x.dtype], _ptr(x), c_ll(x.stride(0)), _ptr(w_gate_up), _ptr(w_down),
+                                          _ptr(act), _ptr(y), _ptr(out), _ptr(ints), _ptr(weight_of), T, experts, top,
+                                          hidden, ff, 0, self._stream())
         self._check(rc, "moe_experts")
-        self.launches += 4                                     # three routing kernels, two products, the sum
+        self.launches += 2
         return out

@@ -43,9 +43,13 @@ class MixtureOfExperts:
             return bind_matrix(torch.stack([weights[n["expert"].format(e) + n[role]] for e in range(spec.experts)]), rt)
 
         self.w_router = bind_matrix(weights[n["router"]], rt)
-        self.w_gate, self.w_up, self.w_down = stack("gate"), stack("up"), stack("down")
+        # an expert's gate rows and behind them its up rows: one matrix [experts, 2 ff, hidden], so that one grouped
+        # product reads the rows once
+        self.w_gate_up = bind_matrix(torch.cat([torch.stack([weights[n["expert"].format(e) + n[r]]
+                                                             for e in range(spec.experts)]) for r in ("gate", "up")], dim=1), rt)
+        self.w_down = stack("down")
 
     def forward(self, x):
         ops = self.rt.ops
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32)      # [T, experts], 32-bit
-        return ops.moe_experts(x, logits, self.w_gate, self.w_up, self.w_down, self.spec.top)
+        return ops.moe_experts(x, logits, self.w_gate_up, self.w_down, self.spec.top)

@@ -278,7 +278,9 @@ class FakeOps:
             out[t] = o
         return out.to(q.dtype)
 
-    def moe_experts(self, x, logits, w_gate, w_up, w_down, top):
+    def moe_experts(self, x, logits, w_gate_up, w_down, top):
+        ff = w_gate_up.shape[1] // 2
+        w_gate, w_up = w_gate_up[:, :ff], w_gate_up[:, ff:]
         val, idx = torch.topk(logits, top, dim=-1)
         wt = torch.softmax(val, dim=-1)
         out = torch.zeros(x.shape, dtype=torch.float32)

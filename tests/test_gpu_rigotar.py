@@ -126,13 +126,16 @@ def test_routed_experts_with_decided_logits(dtype):
     from pih_b200.kernels import get_ops
     ops = get_ops(torch.device(DEV))
     g = torch.Generator().manual_seed(6)
-    rows, hidden, ff, experts, top = 150, 40, 72, 9, 3
+    rows, hidden, ff, experts, top = 300, 40, 72, 9, 3
     x = (torch.randn(rows, hidden, generator=g) * 0.8).to(dtype)
     wg, wu = [(torch.randn(experts, ff, hidden, generator=g) * 0.2).to(dtype) for _ in range(2)]
     wd = (torch.randn(experts, hidden, ff, generator=g) * 0.2).to(dtype)
     logits = torch.stack([torch.randperm(experts, generator=g).float() * 0.7 - 2.0 for _ in range(rows)])
-    got = ops.moe_experts(x.to(DEV), logits.to(DEV), wg.to(DEV).contiguous(), wu.to(DEV).contiguous(),
-                          wd.to(DEV).contiguous(), top).double().cpu()
+    wgu = torch.cat([wg, wu], dim=1).to(DEV).contiguous()
+    got = ops.moe_experts(x.to(DEV), logits.to(DEV), wgu, wd.to(DEV).contiguous(), top).double().cpu()
+    ops.check_errors()
+    # few rows take the kernel that streams the chosen experts' rows; many rows in bfloat16 the library's grouped product
+    few = ops.moe_experts(x[:5].to(DEV), logits[:5].to(DEV), wgu, wd.to(DEV).contiguous(), top).double().cpu()
     ops.check_errors()
     w = {"router": None}
     val, idx = torch.topk(logits.double(), top, dim=-1)
@@ -145,6 +148,7 @@ def test_routed_experts_with_decided_logits(dtype):
             ref[t] += wt[t, j] * (a @ wd[e].double().T)
     tol = 1e-5 if dtype == torch.float32 else 2e-2
     assert float((got - ref).abs().max()) < tol * float(ref.abs().max())
+    assert float((few - ref[:5]).abs().max()) < tol * float(ref.abs().max())
     assert len(set(idx.flatten().tolist())) == experts                    # every expert has rows, unequally many
 
 
