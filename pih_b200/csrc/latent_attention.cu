@@ -12,7 +12,8 @@
 //
 //   latent_write              c = rmsnorm(raw latent) * w  ->  the paged cache [pages, page_size, rank]
 //   latent_attention_generic  one warp a (row, head), keys in order: any rank up to 512; the 32-bit path
-//   latent_attention_split    a block a (row, part of its keys, 8 heads) and a merge: the serving path
+//   latent_attention_split    a block a (row, part of its keys, 8 heads) and a merge: bf16, any rank
+//   latent_attention_mma      the same cut on tensor cores (the heads are the rows of the MMA): bf16, rank 64 .. 512
 #include "common.cuh"
 
 namespace pih {
@@ -216,6 +217,175 @@ latent_attention_split_kernel(const T* __restrict__ q, const T* __restrict__ cac
   }
 }
 
+
+// ---- the tensor-core kernel (bf16, rank 64 / 128 / 192 / 256 / 384 / 512) ------------------------------------------------------
+// Block (row, split of the row's keys, group of 16 heads), 8 warps.  The 16 heads of the row are the 16 rows of an
+// m16n8k16 MMA: scores S[16 heads x 16 keys] = Q'[16 x rank] . C^T and sums O'[16 x rank] += P[16 x 16] . C[16 x rank],
+// so one tile of latents feeds every head's score AND weighted sum.  A tile of 128 latents is staged in shared memory
+// (16-byte copies, padded pitch); warp w takes keys 16 w .. 16 w + 15 of every tile and runs a softmax stream of its
+// own over them (32-bit maximum, sum and accumulators in registers; P goes from the score accumulators straight into
+// the A operand).  Each warp leaves (maximum, sum, weighted sum) per head as one more split for latent_merge.
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  const uint32_t a = static_cast<uint32_t>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+constexpr int kMmaTileKeys = 128;
+
+template <int kRank, int kOut>
+__global__ void __launch_bounds__(256)
+latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
+                            const int* __restrict__ block_table, int table_width, const int* __restrict__ request_of_row,
+                            const int* __restrict__ positions, float* __restrict__ partial, int heads, int page_size,
+                            int num_pages, float scale, int window, int splits, uint32_t* err) {
+  typedef __nv_bfloat16 bf;
+  constexpr int kPitch = kRank + 8;                              // elements; rows 16 bytes apart in the banks
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ long long src_row[kMmaTileKeys];
+  wait_for_prior_kernels();
+  launch_dependents();
+  // a latent wider than 256: the block computes every score but only kOut of the sum's columns (the accumulators of
+  // all of them would not fit a thread's registers); blockIdx.z counts (group of heads, stretch of columns)
+  constexpr int kStretches = kRank / kOut;
+  const int row = blockIdx.x, split = blockIdx.y, h0 = (blockIdx.z / kStretches) * 16;
+  const int cbase = (blockIdx.z % kStretches) * kOut;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int req = request_of_row[row];
+  if (req < 0) return;                                           // a row of padding
+  bf* Qs = reinterpret_cast<bf*>(smem_raw);                      // [16][kPitch]
+  bf* tile = Qs + 16 * kPitch;                                   // [128][kPitch]
+  const int pos = positions[row];
+  const int first = window > 0 ? max(0, pos - window + 1) : 0;
+  const int chunk = (((pos - first + 1) + splits - 1) / splits + kMmaTileKeys - 1) / kMmaTileKeys * kMmaTileKeys;
+  const int k0 = first + split * chunk, k1 = min(pos + 1, k0 + chunk);
+  constexpr int kUnits = kRank / 8;                              // 16-byte units a row
+  for (int i = tid; i < 16 * kUnits; i += 256) {
+    const int hh = i / kUnits, un = i - hh * kUnits;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (h0 + hh < heads) v = *reinterpret_cast<const uint4*>(q + (static_cast<long long>(row) * heads + h0 + hh) * kRank + un * 8);
+    *reinterpret_cast<uint4*>(Qs + hh * kPitch + un * 8) = v;
+  }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+  float O[kOut / 8][4];
+#pragma unroll
+  for (int n = 0; n < kOut / 8; ++n) { O[n][0] = O[n][1] = O[n][2] = O[n][3] = 0.0f; }
+  const int* table = block_table + static_cast<long long>(req) * table_width;
+  const int mi = lane >> 3, lr = lane & 7;
+  for (int t0 = k0; t0 < k1; t0 += kMmaTileKeys) {
+    __syncthreads();                                             // the tile before this one has been used
+    if (tid < kMmaTileKeys) {
+      const int key = t0 + tid;
+      long long src = -1;
+      if (key < k1) {
+        const int pi = key / page_size;
+        const int page = pi < table_width ? table[pi] : -1;
+        if (page < 0 || page >= num_pages) publish_error(err, kRowWithoutPage);
+        else src = (static_cast<long long>(page) * page_size + (key - pi * page_size)) * kRank;
+      }
+      src_row[tid] = src;
+    }
+    __syncthreads();
+    for (int i = tid; i < kMmaTileKeys * kUnits; i += 256) {
+      const int j = i / kUnits, un = i - j * kUnits;
+      const long long src = src_row[j];
+      uint4 v = make_uint4(0u, 0u, 0u, 0u);
+      if (src >= 0) v = *reinterpret_cast<const uint4*>(cache + src + un * 8);
+      *reinterpret_cast<uint4*>(tile + j * kPitch + un * 8) = v;
+    }
+    __syncthreads();
+    const int kl = warp * 16;                                    // this warp's keys within the tile
+    if (t0 + kl >= k1) continue;
+    float S[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+#pragma unroll
+    for (int ks = 0; ks < kRank / 16; ++ks) {
+      uint32_t a[4], b[4];
+      ldmatrix_x4(a, Qs + (lr + (mi & 1) * 8) * kPitch + ks * 16 + (mi >> 1) * 8);
+      ldmatrix_x4(b, tile + (kl + lr + (mi >> 1) * 8) * kPitch + ks * 16 + (mi & 1) * 8);
+      mma_bf16(S[0], a, b[0], b[1]);
+      mma_bf16(S[1], a, b[2], b[3]);
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int kk = kl + nt * 8 + 2 * t4 + (c & 1);
+        const bool valid = t0 + kk < k1 && src_row[kk] >= 0;
+        S[nt][c] = valid ? S[nt][c] * scale : -INFINITY;
+        if (c < 2) mx0 = fmaxf(mx0, S[nt][c]); else mx1 = fmaxf(mx1, S[nt][c]);
+      }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+    const float corr0 = n0 == -INFINITY ? 1.0f : expf(m0 - n0), corr1 = n1 == -INFINITY ? 1.0f : expf(m1 - n1);
+    float sum0 = 0.0f, sum1 = 0.0f;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float nn = c < 2 ? n0 : n1;
+        const float pv = nn == -INFINITY ? 0.0f : expf(S[nt][c] - nn);
+        S[nt][c] = pv;
+        if (c < 2) sum0 += pv; else sum1 += pv;
+      }
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+    l0 = fmaf(l0, corr0, sum0);
+    l1 = fmaf(l1, corr1, sum1);
+    m0 = n0;
+    m1 = n1;
+    uint32_t pa[4];
+    pa[0] = pack_bf16(S[0][0], S[0][1]);
+    pa[1] = pack_bf16(S[0][2], S[0][3]);
+    pa[2] = pack_bf16(S[1][0], S[1][1]);
+    pa[3] = pack_bf16(S[1][2], S[1][3]);
+#pragma unroll
+    for (int nb = 0; nb < kOut / 16; ++nb) {
+      uint32_t b[4];
+      ldmatrix_x4_trans(b, tile + (kl + lr + (mi & 1) * 8) * kPitch + cbase + nb * 16 + (mi >> 1) * 8);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        float (&o)[4] = O[2 * nb + half];
+        o[0] *= corr0; o[1] *= corr0; o[2] *= corr1; o[3] *= corr1;
+        mma_bf16(o, pa, b[2 * half], b[2 * half + 1]);
+      }
+    }
+  }
+  const int parts = splits * 8;
+#pragma unroll
+  for (int hr = 0; hr < 2; ++hr) {
+    const int h = h0 + g + hr * 8;
+    if (h >= heads) continue;
+    float* dst = partial + ((static_cast<long long>(row) * heads + h) * parts + split * 8 + warp) * (kRank + 2);
+    if (t4 == 0 && cbase == 0) { dst[0] = hr ? m1 : m0; dst[1] = hr ? l1 : l0; }
+#pragma unroll
+    for (int n = 0; n < kOut / 8; ++n) {
+      dst[2 + cbase + n * 8 + 2 * t4] = O[n][2 * hr];
+      dst[2 + cbase + n * 8 + 2 * t4 + 1] = O[n][2 * hr + 1];
+    }
+  }
+}
+
 // One warp a (row, head): the splits in order, from the sink.
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -363,6 +533,47 @@ extern "C" int pih_latent_attention_split(int dtype, const void* q, const void* 
   else return PIH_ERR_BAD_ARGUMENT;
 #undef PIH_LS
 #undef PIH_LS1
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+// The tensor-core kernel: bf16, rank 64, 128, 192, 256, 384 or 512.  partial: fp32 scratch, rows * heads * 8 * splits * (rank + 2).
+extern "C" int pih_latent_attention_mma(const void* q, const void* gate, long long ldg, const void* sink, const void* cache,
+                                        const void* block_table, int table_width, const void* request_of_row,
+                                        const void* positions, void* partial, void* out, int rows, int heads, int rank,
+                                        int page_size, int num_pages, float scale, int window, int splits, void* err,
+                                        void* stream) {
+  if (rows <= 0) return 0;
+  if ((rank != 64 && rank != 128 && rank != 192 && rank != 256 && rank != 384 && rank != 512) || splits < 1 ||
+      rows > 65535 * 32)
+    return PIH_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t smem = (16 + kMmaTileKeys) * static_cast<size_t>(rank + 8) * 2;
+  dim3 grid(rows, splits, (heads + 15) / 16 * (rank > 256 ? 2 : 1));
+  const long long items = static_cast<long long>(rows) * heads;
+#define PIH_LM(R, C)                                                                                                    \
+  do {                                                                                                                 \
+    if (smem > 48 * 1024)                                                                                              \
+      cudaFuncSetAttribute(latent_attention_mma_kernel<R, C>, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
+                           static_cast<int>(smem));                                                                    \
+    launch_kernel(latent_attention_mma_kernel<R, C>, grid, dim3(256), smem, s, static_cast<const bf16*>(q),               \
+                  static_cast<const bf16*>(cache), static_cast<const int*>(block_table), table_width,                  \
+                  static_cast<const int*>(request_of_row), static_cast<const int*>(positions),                         \
+                  static_cast<float*>(partial), heads, page_size, num_pages, scale, window, splits,                    \
+                  static_cast<uint32_t*>(err));                                                                        \
+  } while (0)
+  if (rank == 64) PIH_LM(64, 64);
+  else if (rank == 128) PIH_LM(128, 128);
+  else if (rank == 192) PIH_LM(192, 192);
+  else if (rank == 256) PIH_LM(256, 256);
+  else if (rank == 384) PIH_LM(384, 192);
+  else PIH_LM(512, 256);
+#undef PIH_LM
+  PIH_LAUNCH_CHECK();
+  launch_kernel(latent_merge_kernel<bf16>, dim3(static_cast<unsigned>((items + 3) / 4)), dim3(128), 0, s,
+                static_cast<const float*>(partial), static_cast<const bf16*>(gate), ldg, static_cast<const float*>(sink),
+                static_cast<const int*>(request_of_row), static_cast<bf16*>(out), rows, heads, rank, splits * 8,
+                static_cast<uint32_t*>(err));
   PIH_LAUNCH_CHECK();
   return 0;
 }

@@ -234,24 +234,42 @@ __global__ void delta_recurrence_kernel(const float* __restrict__ qn, const floa
 }
 
 // The same recurrence with S in registers, for the key sizes that have an instance.  Block (request, head, 32 value
-// columns) of 128 threads: thread (column c = tid / 4, part p = tid % 4) holds rows p * kDim / 4 ... of column c, so the
-// four parts of a column sit in neighbouring lanes and meet through two shuffles.  k and q of a token are staged in
-// shared memory (two buffers, one barrier a token); the next token's k, q, v, decay and write strength are fetched
-// while this token is computed.  The order of the additions is fixed by the kernel, not by the step's make-up.
+// columns); a column of S is held by 8 threads (4 for small keys), thread (column c = tid / parts, part p = tid % parts)
+// the rows p * kDim / parts ..., so the parts of a column sit in neighbouring lanes and meet through shuffles.  What the recurrence reads of a
+// token (k, q, the block's 32 values, decay, write strength) is staged in shared memory a chunk of tokens at a time,
+// two buffers: the next chunk's numbers are copied asynchronously while this chunk is computed, so no load from
+// memory and only one barrier a chunk lie on the chain from token to token.  The order of the
+// additions is fixed by the kernel, not by the step's make-up or by where a chunk begins.
+__device__ __forceinline__ void async_copy_16(void* smem_dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(src));
+}
+__device__ __forceinline__ void async_copy_4(void* smem_dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(src));
+}
+__device__ __forceinline__ void async_copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void async_copies_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 template <typename T, int kDim>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kDim >= 64 ? 256 : 128)
 delta_recurrence_reg_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const T* __restrict__ v,
                             long long ldv, const float* __restrict__ decay, const float* __restrict__ beta,
                             float* __restrict__ out, float* __restrict__ state, long long state_stride,
                             const int* __restrict__ cu_q, const int* __restrict__ state_slots, int heads, int kv_heads,
                             int vdim) {
-  constexpr int kRows = kDim / 4;                 // rows of S a thread holds
-  constexpr int kFetch = (2 * kDim + 127) / 128;  // numbers of k|q a thread fetches
-  __shared__ __align__(16) float kq[2][2 * kDim];
+  constexpr int kParts = kDim >= 64 ? 8 : 4;              // threads a column of S
+  constexpr int kThreads = 32 * kParts;
+  constexpr int kRows = kDim / kParts;                    // rows of S a thread holds
+  constexpr int kSeg = kRows + 4;                         // a part's stretch of k (or q) in the staging buffer: the parts'
+                                                          // 16-byte reads fall into different banks
+  constexpr int kChunk = kDim <= 128 ? 16 : 8;            // tokens staged at a time (even)
+  constexpr int kVWords = 32 * sizeof(T) / 4;             // the block's 32 values of a token, in 32-bit words
+  constexpr int kTok = 2 * kParts * kSeg + 4 + kVWords;   // words staged a token: k | q | decay - 1, write strength, pad | values
+  constexpr int kCopies = 2 * (kDim / 4) + 2 + kVWords;   // asynchronous copies a token
+  extern __shared__ __align__(16) float stage[];          // [2][kChunk][kTok]
   wait_for_prior_kernels();
   launch_dependents();
   const int r = blockIdx.x, h = blockIdx.y;
-  const int tid = threadIdx.x, part = tid & 3, col = blockIdx.z * 32 + (tid >> 2);
+  const int tid = threadIdx.x, part = tid % kParts, cl = tid / kParts, col0 = blockIdx.z * 32, col = col0 + cl;
   const int lo = cu_q[r], hi = cu_q[r + 1];
   const int slot = state_slots[r];
   if (hi <= lo || slot < 0) return;
@@ -261,64 +279,93 @@ delta_recurrence_reg_kernel(const float* __restrict__ qn, const float* __restric
   float S[kRows];
 #pragma unroll
   for (int i = 0; i < kRows; ++i) S[i] = live ? Sg[static_cast<long long>(i) * vdim + col] : 0.0f;
-  auto fetch = [&](int t, int e) -> float {
-    const int idx = tid + e * 128;
-    if (idx >= 2 * kDim) return 0.0f;
-    const float* src = idx < kDim ? kn : qn;
-    return src[(static_cast<long long>(t) * kv_heads + kh) * kDim + (idx < kDim ? idx : idx - kDim)];
-  };
-  float nxt[kFetch];
-#pragma unroll
-  for (int e = 0; e < kFetch; ++e) nxt[e] = fetch(lo, e);
-  float gm1_n = decay[static_cast<long long>(lo) * heads + h], b_n = beta[static_cast<long long>(lo) * heads + h];
-  float v_n = live ? to_float<T>(v[static_cast<long long>(lo) * ldv + static_cast<long long>(h) * vdim + col]) : 0.0f;
-  for (int t = lo; t < hi; ++t) {
-    float* cur = kq[t & 1];
-#pragma unroll
-    for (int e = 0; e < kFetch; ++e)
-      if (tid + e * 128 < 2 * kDim) cur[tid + e * 128] = nxt[e];
-    const float gm1 = gm1_n, b = b_n, vj = v_n;
-    __syncthreads();
-    if (t + 1 < hi) {
-#pragma unroll
-      for (int e = 0; e < kFetch; ++e) nxt[e] = fetch(t + 1, e);
-      gm1_n = decay[static_cast<long long>(t + 1) * heads + h];
-      b_n = beta[static_cast<long long>(t + 1) * heads + h];
-      v_n = live ? to_float<T>(v[static_cast<long long>(t + 1) * ldv + static_cast<long long>(h) * vdim + col]) : 0.0f;
+  // the copies of the chunk that starts at token t0, into buffer b: straight from memory into shared memory, so that
+  // they are under way while the chunk before is computed
+  auto issue = [&](int t0, int b) {
+    const int n_tok = min(kChunk, hi - t0);
+    for (int i = tid; i < n_tok * kCopies; i += kThreads) {
+      const int tok = i / kCopies, c = i - tok * kCopies;
+      const int t = t0 + tok;
+      float* dst = stage + (b * kChunk + tok) * kTok;
+      if (c < 2 * (kDim / 4)) {
+        const bool is_q = c >= kDim / 4;
+        const int e = (is_q ? c - kDim / 4 : c) * 4;             // element of k (or q)
+        const float* src = (is_q ? qn : kn) + (static_cast<long long>(t) * kv_heads + kh) * kDim + e;
+        async_copy_16(dst + (is_q ? kParts * kSeg : 0) + (e / kRows) * kSeg + e % kRows, src);
+      } else if (c < 2 * (kDim / 4) + 2) {
+        const int which = c - 2 * (kDim / 4);
+        async_copy_4(dst + 2 * kParts * kSeg + which, (which ? beta : decay) + static_cast<long long>(t) * heads + h);
+      } else {
+        const int w = c - 2 * (kDim / 4) - 2;                    // word w holds 4 / sizeof(T) values
+        const int first_col = col0 + w * (4 / static_cast<int>(sizeof(T)));
+        if (first_col < vdim)
+          async_copy_4(dst + 2 * kParts * kSeg + 4 + w,
+                       v + static_cast<long long>(t) * ldv + static_cast<long long>(h) * vdim + first_col);
+      }
     }
-    const float* k = cur + part * kRows;
-    const float* q = cur + kDim + part * kRows;
+    async_copies_commit();
+  };
+  // a token's numbers from the staging buffer into registers, one token ahead of the arithmetic
+  struct Tok { float k[kRows], q[kRows], gm1, b, v; };
+  auto load = [&](Tok& x, const float* cur) {
+#pragma unroll
+    for (int i = 0; i < kRows; i += 4) {
+      const float4 k4 = *reinterpret_cast<const float4*>(cur + part * kSeg + i);
+      const float4 q4 = *reinterpret_cast<const float4*>(cur + kParts * kSeg + part * kSeg + i);
+      x.k[i] = k4.x; x.k[i + 1] = k4.y; x.k[i + 2] = k4.z; x.k[i + 3] = k4.w;
+      x.q[i] = q4.x; x.q[i + 1] = q4.y; x.q[i + 2] = q4.z; x.q[i + 3] = q4.w;
+    }
+    x.gm1 = cur[2 * kParts * kSeg];
+    x.b = cur[2 * kParts * kSeg + 1];
+    x.v = to_float<T>(reinterpret_cast<const T*>(cur + 2 * kParts * kSeg + 4)[cl]);
+  };
+  auto reduce = [&](float x) {
+    x += __shfl_xor_sync(0xffffffffu, x, 1);
+    x += __shfl_xor_sync(0xffffffffu, x, 2);
+    if (kParts == 8) x += __shfl_xor_sync(0xffffffffu, x, 4);
+    return x;
+  };
+  auto compute = [&](const Tok& x, int t) {
     float a0 = 0.0f, a1 = 0.0f;
 #pragma unroll
-    for (int i = 0; i < kRows; i += 4) {
-      const float4 k4 = *reinterpret_cast<const float4*>(k + i);
-      a0 = fmaf(S[i + 0], k4.x, a0);
-      a1 = fmaf(S[i + 1], k4.y, a1);
-      a0 = fmaf(S[i + 2], k4.z, a0);
-      a1 = fmaf(S[i + 3], k4.w, a1);
+    for (int i = 0; i < kRows; i += 2) {
+      a0 = fmaf(S[i], x.k[i], a0);
+      a1 = fmaf(S[i + 1], x.k[i + 1], a1);
     }
-    float dot = a0 + a1;
-    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-    dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-    const float u = b * (vj - fmaf(gm1, dot, dot));
+    const float dot = reduce(a0 + a1);
+    const float u = x.b * (x.v - fmaf(x.gm1, dot, dot));
     float o0 = 0.0f, o1 = 0.0f;
 #pragma unroll
-    for (int i = 0; i < kRows; i += 4) {
-      const float4 k4 = *reinterpret_cast<const float4*>(k + i);
-      const float4 q4 = *reinterpret_cast<const float4*>(q + i);
-      S[i + 0] = fmaf(k4.x, u, fmaf(gm1, S[i + 0], S[i + 0]));
-      S[i + 1] = fmaf(k4.y, u, fmaf(gm1, S[i + 1], S[i + 1]));
-      S[i + 2] = fmaf(k4.z, u, fmaf(gm1, S[i + 2], S[i + 2]));
-      S[i + 3] = fmaf(k4.w, u, fmaf(gm1, S[i + 3], S[i + 3]));
-      o0 = fmaf(S[i + 0], q4.x, o0);
-      o1 = fmaf(S[i + 1], q4.y, o1);
-      o0 = fmaf(S[i + 2], q4.z, o0);
-      o1 = fmaf(S[i + 3], q4.w, o1);
+    for (int i = 0; i < kRows; i += 2) {
+      S[i] = fmaf(x.k[i], u, fmaf(x.gm1, S[i], S[i]));
+      S[i + 1] = fmaf(x.k[i + 1], u, fmaf(x.gm1, S[i + 1], S[i + 1]));
+      o0 = fmaf(S[i], x.q[i], o0);
+      o1 = fmaf(S[i + 1], x.q[i + 1], o1);
     }
-    float o = o0 + o1;
-    o += __shfl_xor_sync(0xffffffffu, o, 1);
-    o += __shfl_xor_sync(0xffffffffu, o, 2);
+    const float o = reduce(o0 + o1);
     if (live && part == 0) out[(static_cast<long long>(t) * heads + h) * vdim + col] = o;
+  };
+  issue(lo, 0);
+  async_copies_wait();
+  __syncthreads();
+  int buf = 0;
+  for (int t0 = lo; t0 < hi; t0 += kChunk) {
+    if (t0 + kChunk < hi) issue(t0 + kChunk, buf ^ 1);
+    const int n_tok = min(kChunk, hi - t0);
+    const float* base = stage + buf * kChunk * kTok;
+    Tok x0, x1;
+    load(x0, base);
+    for (int tok = 0; tok < n_tok; tok += 2) {
+      if (tok + 1 < n_tok) load(x1, base + (tok + 1) * kTok);
+      compute(x0, t0 + tok);
+      if (tok + 1 < n_tok) {
+        if (tok + 2 < n_tok) load(x0, base + (tok + 2) * kTok);
+        compute(x1, t0 + tok + 1);
+      }
+    }
+    async_copies_wait();
+    __syncthreads();
+    buf ^= 1;
   }
   if (live) {
 #pragma unroll
@@ -498,23 +545,34 @@ extern "C" int pih_gated_delta_rule(int dtype, const void* qkv, long long ld, co
   dim3 grid(requests, heads, (vdim + cols - 1) / cols);
   if (grid.y > 65535 || grid.z > 65535) return PIH_ERR_UNSUPPORTED;
   const long long qk_size = static_cast<long long>(kv_heads) * dim;
+  int dim_instance = dim;
 #define PIH_DELTA_REG(T, D)                                                                                            \
-  launch_kernel(delta_recurrence_reg_kernel<T, D>, dim3(requests, heads, (vdim + 31) / 32), dim3(128), 0, s,           \
-                static_cast<const float*>(qn), static_cast<const float*>(kn), static_cast<const T*>(qkv) + 2 * qk_size, \
-                ld, static_cast<const float*>(decay), static_cast<const float*>(beta), static_cast<float*>(out),       \
-                static_cast<float*>(state), state_stride, static_cast<const int*>(cu_q),                               \
-                static_cast<const int*>(state_slots), heads, kv_heads, vdim)
+  do {                                                                                                                 \
+    const int parts = (D) >= 64 ? 8 : 4;                                                                               \
+    const size_t staged = 2 * static_cast<size_t>((D) <= 128 ? 16 : 8) *                                               \
+                          (2 * parts * ((D) / parts + 4) + 4 + 32 * sizeof(T) / 4) * sizeof(float);                    \
+    if (staged > 48 * 1024)                                                                                            \
+      cudaFuncSetAttribute(delta_recurrence_reg_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,             \
+                           static_cast<int>(staged));                                                                  \
+    launch_kernel(delta_recurrence_reg_kernel<T, D>, dim3(requests, heads, (vdim + 31) / 32), dim3(32 * parts), staged, s, \
+                  static_cast<const float*>(qn), static_cast<const float*>(kn),                                        \
+                  static_cast<const T*>(qkv) + 2 * qk_size, ld, static_cast<const float*>(decay),                      \
+                  static_cast<const float*>(beta), static_cast<float*>(out), static_cast<float*>(state), state_stride, \
+                  static_cast<const int*>(cu_q), static_cast<const int*>(state_slots), heads, kv_heads, vdim);         \
+  } while (0)
 #define PIH_DELTA(T)                                                                                                   \
   do {                                                                                                                 \
     launch_kernel(delta_prepare_kernel<T>, dim3(rows), dim3(128), 0, s, static_cast<const T*>(qkv), ld,                \
                   static_cast<const T*>(ba), ldb, static_cast<const float*>(decay_log),                                \
                   static_cast<const float*>(decay_bias), qn, kn, decay, beta, heads, kv_heads, dim, unit_eps, q_scale); \
     PIH_LAUNCH_CHECK();                                                                                                \
-    if (dim == 16) PIH_DELTA_REG(T, 16);                                                                               \
-    else if (dim == 32) PIH_DELTA_REG(T, 32);                                                                          \
-    else if (dim == 64) PIH_DELTA_REG(T, 64);                                                                          \
-    else if (dim == 128) PIH_DELTA_REG(T, 128);                                                                        \
-    else if (dim == 256) PIH_DELTA_REG(T, 256);                                                                        \
+    const bool words = sizeof(T) == 4 || (ld % 2 == 0 && vdim % 2 == 0);      /* values are copied in 32-bit words */  \
+    if (!words) dim_instance = 0;                                                                                      \
+    if (dim_instance == 16) PIH_DELTA_REG(T, 16);                                                                      \
+    else if (dim_instance == 32) PIH_DELTA_REG(T, 32);                                                                          \
+    else if (dim_instance == 64) PIH_DELTA_REG(T, 64);                                                                          \
+    else if (dim_instance == 128) PIH_DELTA_REG(T, 128);                                                                        \
+    else if (dim_instance == 256) PIH_DELTA_REG(T, 256);                                                                        \
     else {                                                                                                             \
       if (smem > 48 * 1024)                                                                                            \
         cudaFuncSetAttribute(delta_recurrence_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)); \

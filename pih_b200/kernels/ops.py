@@ -107,7 +107,7 @@ class CudaOps:
                      "pih_qk_attention_fused", "pih_gemm_tcgen05_pair", "pih_set_attention_side_by_side", "pih_set_skinny_rule",
                      "pih_gemm_simt_batched", "pih_embedding_stream", "pih_rmsnorm_stream", "pih_causal_conv",
                      "pih_gated_delta_rule", "pih_gated_rmsnorm", "pih_rglru_scan", "pih_latent_write",
-                     "pih_latent_attention_generic", "pih_moe_route", "pih_moe_experts", "pih_moe_combine_bf16", "pih_latent_attention_split", "pih_latent_attention_splits"):
+                     "pih_latent_attention_generic", "pih_moe_route", "pih_moe_experts", "pih_moe_combine_bf16", "pih_latent_attention_split", "pih_latent_attention_splits", "pih_latent_attention_mma"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
         lib.pih_top_logprobs_scratch_words.restype = c_ll
@@ -633,6 +633,8 @@ class CudaOps:
         self._check(rc, "gemm_simt_batched")
         return out
 
+    latent_mma = True                      # bf16 attention over a latent of rank 64 ... 512: the tensor-core kernel ...
+    latent_mma_min_rows = 64               # ... for steps of more rows than this (a decode step's few rows: the cut kernel)
     latent_split = True                    # bf16 attention over a latent: keys cut into parts (False: the in-order kernel)
     batched_library_min_rows = 1 << 30     # set lower to send bf16 batched products of many rows to the library
 
@@ -724,6 +726,20 @@ class CudaOps:
         num_pages, page_size = cache.shape[0], cache.shape[1]
         assert q.is_contiguous() and (gate is None or gate.stride(1) == 1)
         out = torch.empty_like(q)
+        if q.dtype == torch.bfloat16 and self.latent_mma and rank in (64, 128, 192, 256, 384, 512) and T > self.latent_mma_min_rows:
+            # tensor cores: the row's heads are the rows of the MMA, a tile of latents feeds every head's scores and sums;
+            # a row's keys are cut into ``splits`` parts side by side, and each of a block's 8 warps is a part of its own
+            splits = max(1, min(16, (2 * 148) // max(1, T * (-(-heads // 16)))))
+            partial = torch.empty(T * heads * splits * 8 * (rank + 2), dtype=torch.float32, device=q.device)
+            rc = self.lib.pih_latent_attention_mma(
+                _ptr(q), _ptr(gate), c_ll(gate.stride(0) if gate is not None else 0), _ptr(sink), _ptr(cache),
+                _ptr(block_table), block_table.shape[1], _ptr(step.request_of_row), _ptr(step.positions), _ptr(partial),
+                _ptr(out), T, heads, rank, page_size, num_pages, c_float(scale), int(window), splits, self._err(),
+                self._stream())
+            if rc != -2:
+                self._check(rc, "latent_attention_mma")
+                self.launches += 1
+                return out
         if q.dtype == torch.bfloat16 and self.latent_split and rank % 4 == 0:
             # the serving path: a row's keys are cut into parts that run side by side (as many as fill the GPU for this
             # number of rows) and a tile of latents is fetched once for 8 heads.  The 32-bit path keeps the kernel that
