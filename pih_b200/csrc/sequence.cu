@@ -74,15 +74,18 @@ rmsnorm_stream_kernel(float* __restrict__ h, const TD* __restrict__ delta, const
   }
 }
 
-// Block (32 channels, 8 token lanes) owns a request's rows of 32 channels: it reads the old history, computes every
-// row, and its first token lane writes the new history at the end (no other block touches these numbers).
+// Block (32 channels, 8 token lanes) computes 128 rows of a request for 32 channels; blockIdx.z counts the stretches of
+// 128 rows (launched for the step's row count; stretches beyond a request's rows leave).
 // in(s) = x[s] + in_bias for s >= 0, the history for -(taps-1) <= s < 0 (zeros at the start of a sequence).
-// out[t] = act( sum_j w[c][j] in(t - (taps-1) + j) + out_bias ).
+// out[t] = act( sum_j w[c][j] in(t - (taps-1) + j) + out_bias ).  The history is only read here; causal_conv_history
+// replaces it afterwards.
+constexpr int kConvRows = 128;
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 causal_conv_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ w, const float* __restrict__ in_bias,
                    const float* __restrict__ out_bias, T* __restrict__ out, long long ldo, int channels, int taps,
-                   int activation, float* __restrict__ state, long long state_stride, long long state_offset,
+                   int activation, const float* __restrict__ state, long long state_stride, long long state_offset,
                    const int* __restrict__ cu_q, const int* __restrict__ state_slots) {
   wait_for_prior_kernels();
   launch_dependents();
@@ -90,35 +93,62 @@ causal_conv_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__
   const int c = blockIdx.y * 32 + threadIdx.x;
   const int lo = cu_q[r], n = cu_q[r + 1] - lo;
   const int slot = state_slots[r];
-  if (n <= 0 || slot < 0) return;
-  const bool live = c < channels;
+  const int t_first = blockIdx.z * kConvRows;
+  if (n <= t_first || slot < 0 || c >= channels) return;
   const int hist_n = taps - 1;
-  float* st = state + slot * state_stride + state_offset;       // [taps-1][channels]
-  __shared__ float hist[kMaxTaps][32];
+  const float* st = state + slot * state_stride + state_offset;       // [taps-1][channels]
   float wr[kMaxTaps];
 #pragma unroll
-  for (int j = 0; j < kMaxTaps; ++j)
-    wr[j] = (live && j < taps) ? to_float<T>(w[static_cast<long long>(c) * taps + j]) : 0.0f;
-  if (threadIdx.y == 0)
-    for (int j = 0; j < hist_n; ++j) hist[j][threadIdx.x] = live ? st[static_cast<long long>(j) * channels + c] : 0.0f;
-  const float ib = (live && in_bias != nullptr) ? in_bias[c] : 0.0f;
-  const float ob = (live && out_bias != nullptr) ? out_bias[c] : 0.0f;
-  __syncthreads();                                              // the old history is on chip
-  if (!live) return;
-  auto input = [&](int s) -> float {
-    return s >= 0 ? to_float<T>(x[static_cast<long long>(lo + s) * ldx + c]) + ib : hist[hist_n + s][threadIdx.x];
-  };
-  for (int t = threadIdx.y; t < n; t += blockDim.y) {
+  for (int j = 0; j < kMaxTaps; ++j) wr[j] = j < taps ? to_float<T>(w[static_cast<long long>(c) * taps + j]) : 0.0f;
+  const float ib = in_bias != nullptr ? in_bias[c] : 0.0f;
+  const float ob = out_bias != nullptr ? out_bias[c] : 0.0f;
+  const int t_end = min(n, t_first + kConvRows);
+  for (int t = t_first + threadIdx.y; t < t_end; t += blockDim.y) {
     float acc = 0.0f;
 #pragma unroll
-    for (int j = 0; j < kMaxTaps; ++j)
-      if (j < taps) acc = fmaf(wr[j], input(t - hist_n + j), acc);
+    for (int j = 0; j < kMaxTaps; ++j) {
+      if (j < taps) {
+        const int s = t - hist_n + j;
+        const float v = s >= 0 ? to_float<T>(x[static_cast<long long>(lo + s) * ldx + c]) + ib
+                               : st[static_cast<long long>(hist_n + s) * channels + c];
+        acc = fmaf(wr[j], v, acc);
+      }
+    }
     acc += ob;
     if (activation == 1) acc = acc / (1.0f + expf(-acc));
     out[static_cast<long long>(lo + t) * ldo + c] = from_float<T>(acc);
   }
-  if (threadIdx.y == 0)
-    for (int j = 0; j < hist_n; ++j) st[static_cast<long long>(j) * channels + c] = input(n - hist_n + j);
+}
+
+// Thread a (request, channel): the history becomes the last taps-1 inputs of [old history, the step's rows].
+template <typename T>
+__global__ void __launch_bounds__(128)
+causal_conv_history_kernel(const T* __restrict__ x, long long ldx, const float* __restrict__ in_bias, int channels, int taps,
+                           float* __restrict__ state, long long state_stride, long long state_offset,
+                           const int* __restrict__ cu_q, const int* __restrict__ state_slots) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int r = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int lo = cu_q[r], n = cu_q[r + 1] - lo;
+  const int slot = state_slots[r];
+  if (n <= 0 || slot < 0 || c >= channels) return;
+  const int hist_n = taps - 1;
+  float* st = state + slot * state_stride + state_offset;
+  const float ib = in_bias != nullptr ? in_bias[c] : 0.0f;
+  float keep[kMaxTaps];
+#pragma unroll
+  for (int j = 0; j < kMaxTaps; ++j) {
+    keep[j] = 0.0f;
+    if (j < hist_n) {
+      const int s = n - hist_n + j;
+      keep[j] = s >= 0 ? to_float<T>(x[static_cast<long long>(lo + s) * ldx + c]) + ib
+                       : st[static_cast<long long>(hist_n + s) * channels + c];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < kMaxTaps; ++j)
+    if (j < hist_n) st[static_cast<long long>(j) * channels + c] = keep[j];
 }
 
 // One block a row.  qk: [rows, ld] with q heads at column 0 and k heads at column kv_heads*dim (after convolution and
@@ -442,11 +472,13 @@ rglru_chain_kernel(const float4* __restrict__ coef, T* __restrict__ out, long lo
   if (hi <= lo || slot < 0 || c >= width) return;
   float S = state[slot * state_stride + c];
   constexpr int kAhead = 8;
-  for (int t0 = lo; t0 < hi; t0 += kAhead) {
-    float4 f[kAhead];
+  float4 cur[kAhead], nxt[kAhead];
+  auto fetch = [&](float4 (&f)[kAhead], int t0) {
 #pragma unroll
     for (int i = 0; i < kAhead; ++i)
       f[i] = t0 + i < hi ? coef[static_cast<long long>(t0 + i) * width + c] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  };
+  auto chain = [&](const float4 (&f)[kAhead], int t0) {
 #pragma unroll
     for (int i = 0; i < kAhead; ++i) {
       if (t0 + i < hi) {
@@ -454,6 +486,13 @@ rglru_chain_kernel(const float4* __restrict__ coef, T* __restrict__ out, long lo
         out[static_cast<long long>(t0 + i) * ldo + c] = from_float<T>(S * f[i].w);
       }
     }
+  };
+  fetch(cur, lo);
+  for (int t0 = lo; t0 < hi; t0 += 2 * kAhead) {           // the next eight tokens' numbers are under way during the chain
+    fetch(nxt, t0 + kAhead);
+    chain(cur, t0);
+    fetch(cur, t0 + 2 * kAhead);
+    chain(nxt, t0 + kAhead);
   }
   state[slot * state_stride + c] = S;
 }
@@ -504,17 +543,25 @@ extern "C" int pih_rmsnorm_stream(int delta_dtype, int out_dtype, void* h, const
 extern "C" int pih_causal_conv(int dtype, const void* x, long long ldx, const void* w, const void* in_bias,
                                const void* out_bias, void* out, long long ldo, int channels, int taps, int activation,
                                void* state, long long state_stride, long long state_offset, const void* cu_q,
-                               const void* state_slots, int requests, void* stream) {
-  if (requests <= 0 || channels <= 0) return 0;
+                               const void* state_slots, int rows, int requests, void* stream) {
+  if (requests <= 0 || channels <= 0 || rows <= 0) return 0;
   if (taps < 1 || taps > kMaxTaps) return PIH_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  dim3 grid(requests, (channels + 31) / 32), block(32, 8);
-  if (grid.y > 65535) return PIH_ERR_UNSUPPORTED;
+  dim3 grid(requests, (channels + 31) / 32, (rows + kConvRows - 1) / kConvRows), block(32, 8);
+  dim3 grid_h(requests, (channels + 127) / 128);
+  if (grid.y > 65535 || grid.z > 65535) return PIH_ERR_UNSUPPORTED;
 #define PIH_CONV(T)                                                                                                    \
-  launch_kernel(causal_conv_kernel<T>, grid, block, 0, s, static_cast<const T*>(x), ldx, static_cast<const T*>(w),      \
-                static_cast<const float*>(in_bias), static_cast<const float*>(out_bias), static_cast<T*>(out), ldo,    \
-                channels, taps, activation, static_cast<float*>(state), state_stride, state_offset,                   \
-                static_cast<const int*>(cu_q), static_cast<const int*>(state_slots))
+  do {                                                                                                                 \
+    launch_kernel(causal_conv_kernel<T>, grid, block, 0, s, static_cast<const T*>(x), ldx, static_cast<const T*>(w),    \
+                  static_cast<const float*>(in_bias), static_cast<const float*>(out_bias), static_cast<T*>(out), ldo,  \
+                  channels, taps, activation, static_cast<const float*>(state), state_stride, state_offset,            \
+                  static_cast<const int*>(cu_q), static_cast<const int*>(state_slots));                                \
+    PIH_LAUNCH_CHECK();                                                                                                \
+    if (taps > 1)                                                                                                      \
+      launch_kernel(causal_conv_history_kernel<T>, grid_h, dim3(128), 0, s, static_cast<const T*>(x), ldx,             \
+                    static_cast<const float*>(in_bias), channels, taps, static_cast<float*>(state), state_stride,      \
+                    state_offset, static_cast<const int*>(cu_q), static_cast<const int*>(state_slots));                \
+  } while (0)
   if (dtype == PIH_F32) PIH_CONV(float);
   else if (dtype == PIH_BF16) PIH_CONV(bf16);
   else return PIH_ERR_BAD_ARGUMENT;

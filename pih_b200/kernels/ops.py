@@ -652,8 +652,9 @@ class CudaOps:
         rc = self.lib.pih_causal_conv(_DT[x.dtype], _ptr(x), c_ll(x.stride(0)), _ptr(w), _ptr(in_bias), _ptr(out_bias),
                                       _ptr(out), c_ll(C), C, taps, {None: 0, "silu": 1}[activation], _ptr(state),
                                       c_ll(state.stride(0)), c_ll(state_offset), _ptr(step.cu_q), _ptr(step.state_slots),
-                                      step.num_requests, self._stream())
+                                      T, step.num_requests, self._stream())
         self._check(rc, "causal_conv")
+        self.launches += 1 if taps > 1 else 0                  # (the history's kernel)
         return out
 
     def gated_delta_rule(self, qkv: torch.Tensor, ba: torch.Tensor, *, decay_log, decay_bias, state: torch.Tensor, step,
