@@ -386,47 +386,57 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
   }
 }
 
-// One warp a (row, head): the splits in order, from the sink.
+// One warp a (row, head): the parts' maxima give the common maximum (the sink's logit among them), every part its
+// factor exp(maximum of the part - common maximum) (kept in shared memory), then the sums and the columns, part by part
+// in order.  At most kMergeParts parts.
+constexpr int kMergeParts = 256;
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 latent_merge_kernel(const float* __restrict__ partial, const T* __restrict__ gate, long long ldg,
                     const float* __restrict__ sink, const int* __restrict__ request_of_row, T* __restrict__ out, int rows,
                     int heads, int rank, int splits, uint32_t* err) {
+  __shared__ float factor_of[4][kMergeParts];
   wait_for_prior_kernels();
   launch_dependents();
   const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (item >= static_cast<long long>(rows) * heads) return;
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row = static_cast<int>(item / heads), h = static_cast<int>(item % heads);
   if (request_of_row[row] < 0) return;
-  float m = sink != nullptr ? sink[h] : -INFINITY;
-  float l = sink != nullptr ? 1.0f : 0.0f;
   const float* base = partial + item * splits * (rank + 2);
-  // first the maximum and the sum over the splits, then the columns with each split's factor
-  float m_all = m;
-  for (int s = 0; s < splits; ++s)
+  float m_all = sink != nullptr ? sink[h] : -INFINITY;
+  for (int s = lane; s < splits; s += 32)
     if (base[s * (rank + 2) + 1] > 0.0f) m_all = fmaxf(m_all, base[s * (rank + 2)]);
-  l = l * expf(m - m_all);
-  for (int s = 0; s < splits; ++s) {
+  m_all = warp_max(m_all);
+  float l = 0.0f;
+  for (int s = lane; s < splits; s += 32) {
     const float ls = base[s * (rank + 2) + 1];
-    if (ls > 0.0f) l = fmaf(ls, expf(base[s * (rank + 2)] - m_all), l);
+    const float f = ls > 0.0f ? expf(base[s * (rank + 2)] - m_all) : 0.0f;
+    factor_of[warp][s] = f;
+    l = fmaf(ls, f, l);
   }
+  l = warp_sum(l);
+  if (sink != nullptr) l += expf(sink[h] - m_all);
+  __syncwarp();
   if (!(l > 0.0f) || !isfinite(l)) {
     if (lane == 0) publish_error(err, kAttentionDenominator);
     l = 1.0f;
   }
-  float factor = 1.0f / l;
+  float scale_out = 1.0f / l;
   if (gate != nullptr) {
     const float z = to_float<T>(gate[static_cast<long long>(row) * ldg + h]);
-    factor *= 1.0f / (1.0f + expf(-z));
+    scale_out *= 1.0f / (1.0f + expf(-z));
   }
   for (int i = lane; i < rank; i += 32) {
-    float a = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-      const float* ps = base + s * (rank + 2);
-      if (ps[1] > 0.0f) a = fmaf(ps[2 + i], expf(ps[0] - m_all), a);
+    float a0 = 0.0f, a1 = 0.0f;
+    int s = 0;
+    for (; s + 2 <= splits; s += 2) {
+      a0 = fmaf(base[s * (rank + 2) + 2 + i], factor_of[warp][s], a0);
+      a1 = fmaf(base[(s + 1) * (rank + 2) + 2 + i], factor_of[warp][s + 1], a1);
     }
-    out[item * rank + i] = from_float<T>(a * factor);
+    if (s < splits) a0 = fmaf(base[s * (rank + 2) + 2 + i], factor_of[warp][s], a0);
+    out[item * rank + i] = from_float<T>((a0 + a1) * scale_out);
   }
 }
 
@@ -499,7 +509,8 @@ extern "C" int pih_latent_attention_split(int dtype, const void* q, const void* 
                                           int rows, int heads, int rank, int page_size, int num_pages, float scale,
                                           int window, int splits, void* err, void* stream) {
   if (rows <= 0) return 0;
-  if (rank > 32 * kLatentPerLane || rank % 4 || splits < 1 || rows > 65535 * 32) return PIH_ERR_UNSUPPORTED;
+  if (rank > 32 * kLatentPerLane || rank % 4 || splits < 1 || splits > kMergeParts || rows > 65535 * 32)
+    return PIH_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int esize = dtype == PIH_F32 ? 4 : 2;
   const size_t smem = 8 * static_cast<size_t>(rank) * 4 + 32 * static_cast<size_t>(rank + (esize == 2 ? 2 : 1)) * esize;
@@ -545,7 +556,7 @@ extern "C" int pih_latent_attention_mma(const void* q, const void* gate, long lo
                                         void* stream) {
   if (rows <= 0) return 0;
   if ((rank != 64 && rank != 128 && rank != 192 && rank != 256 && rank != 384 && rank != 512) || splits < 1 ||
-      rows > 65535 * 32)
+      splits * 8 > kMergeParts || rows > 65535 * 32)
     return PIH_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t smem = (16 + kMmaTileKeys) * static_cast<size_t>(rank + 8) * 2;
