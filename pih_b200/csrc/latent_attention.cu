@@ -429,14 +429,10 @@ latent_merge_kernel(const float* __restrict__ partial, const T* __restrict__ gat
     scale_out *= 1.0f / (1.0f + expf(-z));
   }
   for (int i = lane; i < rank; i += 32) {
-    float a0 = 0.0f, a1 = 0.0f;
-    int s = 0;
-    for (; s + 2 <= splits; s += 2) {
-      a0 = fmaf(base[s * (rank + 2) + 2 + i], factor_of[warp][s], a0);
-      a1 = fmaf(base[(s + 1) * (rank + 2) + 2 + i], factor_of[warp][s + 1], a1);
-    }
-    if (s < splits) a0 = fmaf(base[s * (rank + 2) + 2 + i], factor_of[warp][s], a0);
-    out[item * rank + i] = from_float<T>((a0 + a1) * scale_out);
+    float a = 0.0f;
+#pragma unroll 8
+    for (int s = 0; s < splits; ++s) a = fmaf(base[s * (rank + 2) + 2 + i], factor_of[warp][s], a);   // (loads run ahead)
+    out[item * rank + i] = from_float<T>(a * scale_out);
   }
 }
 

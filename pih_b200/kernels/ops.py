@@ -621,12 +621,10 @@ class CudaOps:
         N = w.shape[1]
         out_dtype = out_dtype or x.dtype
         assert w.shape == (B, N, K) and w.is_contiguous() and x.dtype == w.dtype and x.stride(2) == 1
+        if x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and T >= self.batched_library_min_rows:
+            # many rows in bf16: the library's batched product (32-bit accumulation), as the single products of many rows
+            return torch.bmm(x.transpose(0, 1), w.transpose(1, 2)).transpose(0, 1).contiguous()
         out = torch.empty(T, B, N, dtype=out_dtype, device=x.device)
-        if x.dtype == torch.bfloat16 and T > self.batched_library_min_rows:
-            # many rows in bf16: the library's batched product (32-bit accumulation)
-            torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1)) if out_dtype == x.dtype else \
-                out.copy_(torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out_dtype=torch.float32).transpose(0, 1))
-            return out
         rc = self.lib.pih_gemm_simt_batched(_DT[x.dtype], _DT[out_dtype], _ptr(x), _ptr(w), _ptr(out), T, N, K,
                                             c_ll(x.stride(0)), c_ll(K), c_ll(B * N), B, c_ll(x.stride(1)), c_ll(N * K),
                                             c_ll(N), self._stream())
@@ -636,7 +634,7 @@ class CudaOps:
     latent_mma = True                      # bf16 attention over a latent of rank 64 ... 512: the tensor-core kernel ...
     latent_mma_min_rows = 64               # ... for steps of more rows than this (a decode step's few rows: the cut kernel)
     latent_split = True                    # bf16 attention over a latent: keys cut into parts (False: the in-order kernel)
-    batched_library_min_rows = 1 << 30     # set lower to send bf16 batched products of many rows to the library
+    batched_library_min_rows = 128         # bf16 batched products of at least this many rows are the library's
 
     def causal_conv(self, x: torch.Tensor, w: torch.Tensor, *, step, state: torch.Tensor, state_offset: int,
                     in_bias: Optional[torch.Tensor] = None, out_bias: Optional[torch.Tensor] = None,
