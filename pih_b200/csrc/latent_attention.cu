@@ -386,52 +386,56 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
   }
 }
 
-// One warp a (row, head): the parts' maxima give the common maximum (the sink's logit among them), every part its
-// factor exp(maximum of the part - common maximum) (kept in shared memory), then the sums and the columns, part by part
-// in order.  At most kMergeParts parts.
+// One block a (row, head): the parts' maxima give the common maximum (the sink's logit among them), every part its
+// factor exp(maximum of the part - common maximum) (first warp, kept in shared memory), then a thread a column adds the
+// parts' columns in order, eight loads under way at a time.  At most kMergeParts parts.
 constexpr int kMergeParts = 256;
 
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 latent_merge_kernel(const float* __restrict__ partial, const T* __restrict__ gate, long long ldg,
                     const float* __restrict__ sink, const int* __restrict__ request_of_row, T* __restrict__ out, int rows,
                     int heads, int rank, int splits, uint32_t* err) {
-  __shared__ float factor_of[4][kMergeParts];
+  __shared__ float factor_of[kMergeParts];
+  __shared__ float scale_s;
   wait_for_prior_kernels();
   launch_dependents();
-  const long long item = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (item >= static_cast<long long>(rows) * heads) return;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long item = blockIdx.x;
+  const int lane = threadIdx.x & 31;
   const int row = static_cast<int>(item / heads), h = static_cast<int>(item % heads);
   if (request_of_row[row] < 0) return;
   const float* base = partial + item * splits * (rank + 2);
-  float m_all = sink != nullptr ? sink[h] : -INFINITY;
-  for (int s = lane; s < splits; s += 32)
-    if (base[s * (rank + 2) + 1] > 0.0f) m_all = fmaxf(m_all, base[s * (rank + 2)]);
-  m_all = warp_max(m_all);
-  float l = 0.0f;
-  for (int s = lane; s < splits; s += 32) {
-    const float ls = base[s * (rank + 2) + 1];
-    const float f = ls > 0.0f ? expf(base[s * (rank + 2)] - m_all) : 0.0f;
-    factor_of[warp][s] = f;
-    l = fmaf(ls, f, l);
+  if (threadIdx.x < 32) {
+    float m_all = sink != nullptr ? sink[h] : -INFINITY;
+    for (int s = lane; s < splits; s += 32)
+      if (base[s * (rank + 2) + 1] > 0.0f) m_all = fmaxf(m_all, base[s * (rank + 2)]);
+    m_all = warp_max(m_all);
+    float l = 0.0f;
+    for (int s = lane; s < splits; s += 32) {
+      const float ls = base[s * (rank + 2) + 1];
+      const float f = ls > 0.0f ? expf(base[s * (rank + 2)] - m_all) : 0.0f;
+      factor_of[s] = f;
+      l = fmaf(ls, f, l);
+    }
+    l = warp_sum(l);
+    if (sink != nullptr) l += expf(sink[h] - m_all);
+    if (!(l > 0.0f) || !isfinite(l)) {
+      if (lane == 0) publish_error(err, kAttentionDenominator);
+      l = 1.0f;
+    }
+    float scale_out = 1.0f / l;
+    if (gate != nullptr) {
+      const float z = to_float<T>(gate[static_cast<long long>(row) * ldg + h]);
+      scale_out *= 1.0f / (1.0f + expf(-z));
+    }
+    if (lane == 0) scale_s = scale_out;
   }
-  l = warp_sum(l);
-  if (sink != nullptr) l += expf(sink[h] - m_all);
-  __syncwarp();
-  if (!(l > 0.0f) || !isfinite(l)) {
-    if (lane == 0) publish_error(err, kAttentionDenominator);
-    l = 1.0f;
-  }
-  float scale_out = 1.0f / l;
-  if (gate != nullptr) {
-    const float z = to_float<T>(gate[static_cast<long long>(row) * ldg + h]);
-    scale_out *= 1.0f / (1.0f + expf(-z));
-  }
-  for (int i = lane; i < rank; i += 32) {
+  __syncthreads();
+  const float scale_out = scale_s;
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) {
     float a = 0.0f;
 #pragma unroll 8
-    for (int s = 0; s < splits; ++s) a = fmaf(base[s * (rank + 2) + 2 + i], factor_of[warp][s], a);   // (loads run ahead)
+    for (int s = 0; s < splits; ++s) a = fmaf(base[s * (rank + 2) + 2 + i], factor_of[s], a);   // (loads run ahead)
     out[item * rank + i] = from_float<T>(a * scale_out);
   }
 }
@@ -530,7 +534,7 @@ extern "C" int pih_latent_attention_split(int dtype, const void* q, const void* 
     else if (rank <= 256) PIH_LS1(T, 8);                                                                               \
     else PIH_LS1(T, 16);                                                                                               \
     PIH_LAUNCH_CHECK();                                                                                                \
-    launch_kernel(latent_merge_kernel<T>, dim3(static_cast<unsigned>((items + 3) / 4)), dim3(128), 0, s,               \
+    launch_kernel(latent_merge_kernel<T>, dim3(static_cast<unsigned>(items)), dim3(rank >= 256 ? 256 : (rank + 31) / 32 * 32), 0, s, \
                   static_cast<const float*>(partial), static_cast<const T*>(gate), ldg, static_cast<const float*>(sink), \
                   static_cast<const int*>(request_of_row), static_cast<T*>(out), rows, heads, rank, splits,            \
                   static_cast<uint32_t*>(err));                                                                        \
@@ -577,7 +581,7 @@ extern "C" int pih_latent_attention_mma(const void* q, const void* gate, long lo
   else PIH_LM(512, 256);
 #undef PIH_LM
   PIH_LAUNCH_CHECK();
-  launch_kernel(latent_merge_kernel<bf16>, dim3(static_cast<unsigned>((items + 3) / 4)), dim3(128), 0, s,
+  launch_kernel(latent_merge_kernel<bf16>, dim3(static_cast<unsigned>(items)), dim3(rank >= 256 ? 256 : (rank + 31) / 32 * 32), 0, s,
                 static_cast<const float*>(partial), static_cast<const bf16*>(gate), ldg, static_cast<const float*>(sink),
                 static_cast<const int*>(request_of_row), static_cast<bf16*>(out), rows, heads, rank, splits * 8,
                 static_cast<uint32_t*>(err));

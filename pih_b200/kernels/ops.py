@@ -632,7 +632,7 @@ class CudaOps:
         return out
 
     latent_mma = True                      # bf16 attention over a latent of rank 64 ... 512: the tensor-core kernel ...
-    latent_mma_min_rows = 64               # ... for steps of more rows than this (a decode step's few rows: the cut kernel)
+    latent_mma_min_rows = 0                # ... for steps of more rows than this
     latent_split = True                    # bf16 attention over a latent: keys cut into parts (False: the in-order kernel)
     batched_library_min_rows = 128         # bf16 batched products of at least this many rows are the library's
 

@@ -209,7 +209,6 @@ def test_latent_attention_finds_one_key_among_hundreds(needle, rank, dtype):
     sides of a page border, far back, and the row itself.  Random inputs would average such a key away."""
     from pih_b200.kernels import get_ops
     ops = get_ops(torch.device(DEV))
-    ops.latent_mma_min_rows = 0                                        # (one row: the tensor-core kernel all the same)
     g = torch.Generator().manual_seed(needle)
     heads, n, page = 3, 300, 16
     lat = torch.randn(n, rank, generator=g, dtype=F64) * 0.3
@@ -226,7 +225,6 @@ def test_latent_attention_finds_one_key_among_hundreds(needle, rank, dtype):
     step = _step([n - 1], [0], [0, 1], [0])
     got = ops.latent_attention(q.to(dtype).to(DEV).view(1, heads, rank).contiguous(), gate=gate.to(dtype).to(DEV).view(1, heads),
                                sink=sink.float().to(DEV), cache=cache, block_table=table, step=step, scale=0.5)
-    ops.latent_mma_min_rows = 64
     ops.check_errors()
     ref = _plain_latent_rows(q, lat, sink, gate, 0.5)
     weight_of_needle = torch.softmax((q @ lat.T) * 0.5, dim=1)[:, needle]
