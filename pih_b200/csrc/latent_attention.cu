@@ -247,14 +247,20 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 constexpr int kMmaTileKeys = 128;
 
-template <int kRank, int kOut>
+// kRowsPerBlock = 1: the block is one row (blockIdx.x), its 8 warps take the tile's 8 groups of 16 keys.
+// kRowsPerBlock = 4: the block is 4 consecutive rows of ONE request (blockIdx.x counts the requests' row tiles, found
+// by walking cu_q; blocks beyond the last tile leave), so a tile of latents is fetched once for 4 rows: warp w is row
+// w % 4 and takes every second group of 16 keys.  Parts a (row, head): splits * 8 / kRowsPerBlock.
+template <int kRank, int kOut, int kRowsPerBlock>
 __global__ void __launch_bounds__(256)
 latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ cache,
                             const int* __restrict__ block_table, int table_width, const int* __restrict__ request_of_row,
-                            const int* __restrict__ positions, float* __restrict__ partial, int heads, int page_size,
-                            int num_pages, float scale, int window, int splits, uint32_t* err) {
+                            const int* __restrict__ positions, const int* __restrict__ cu_q, int requests,
+                            float* __restrict__ partial, int heads, int page_size, int num_pages, float scale, int window,
+                            int splits, uint32_t* err) {
   typedef __nv_bfloat16 bf;
   constexpr int kPitch = kRank + 8;                              // elements; rows 16 bytes apart in the banks
+  constexpr int kStreams = 8 / kRowsPerBlock;                    // warps a row, each a stream of its own over keys
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ long long src_row[kMmaTileKeys];
   wait_for_prior_kernels();
@@ -262,25 +268,49 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
   // a latent wider than 256: the block computes every score but only kOut of the sum's columns (the accumulators of
   // all of them would not fit a thread's registers); blockIdx.z counts (group of heads, stretch of columns)
   constexpr int kStretches = kRank / kOut;
-  const int row = blockIdx.x, split = blockIdx.y, h0 = (blockIdx.z / kStretches) * 16;
+  const int split = blockIdx.y, h0 = (blockIdx.z / kStretches) * 16;
   const int cbase = (blockIdx.z % kStretches) * kOut;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
-  const int req = request_of_row[row];
-  if (req < 0) return;                                           // a row of padding
-  bf* Qs = reinterpret_cast<bf*>(smem_raw);                      // [16][kPitch]
-  bf* tile = Qs + 16 * kPitch;                                   // [128][kPitch]
-  const int pos = positions[row];
-  const int first = window > 0 ? max(0, pos - window + 1) : 0;
-  const int chunk = (((pos - first + 1) + splits - 1) / splits + kMmaTileKeys - 1) / kMmaTileKeys * kMmaTileKeys;
-  const int k0 = first + split * chunk, k1 = min(pos + 1, k0 + chunk);
-  constexpr int kUnits = kRank / 8;                              // 16-byte units a row
-  for (int i = tid; i < 16 * kUnits; i += 256) {
-    const int hh = i / kUnits, un = i - hh * kUnits;
-    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-    if (h0 + hh < heads) v = *reinterpret_cast<const uint4*>(q + (static_cast<long long>(row) * heads + h0 + hh) * kRank + un * 8);
-    *reinterpret_cast<uint4*>(Qs + hh * kPitch + un * 8) = v;
+  int row0, n_rows, req;
+  if (kRowsPerBlock == 1) {
+    row0 = blockIdx.x;
+    n_rows = 1;
+    req = request_of_row[row0];
+    if (req < 0) return;                                         // a row of padding
+  } else {
+    int b = blockIdx.x;
+    req = 0;
+    for (; req < requests; ++req) {
+      const int tiles = (cu_q[req + 1] - cu_q[req] + kRowsPerBlock - 1) / kRowsPerBlock;
+      if (b < tiles) break;
+      b -= tiles;
+    }
+    if (req >= requests) return;                                 // beyond the last row tile
+    row0 = cu_q[req] + b * kRowsPerBlock;
+    n_rows = min(kRowsPerBlock, cu_q[req + 1] - row0);
   }
+  bf* Qs = reinterpret_cast<bf*>(smem_raw);                      // [kRowsPerBlock * 16][kPitch]
+  bf* tile = Qs + kRowsPerBlock * 16 * kPitch;                   // [128][kPitch]
+  // the block's keys: from the first row's first key to the last row's position, cut into ``splits``
+  const int pos_last = positions[row0 + n_rows - 1];
+  const int first_0 = window > 0 ? max(0, positions[row0] - window + 1) : 0;
+  const int chunk = (((pos_last - first_0 + 1) + splits - 1) / splits + kMmaTileKeys - 1) / kMmaTileKeys * kMmaTileKeys;
+  const int k0 = first_0 + split * chunk, k1 = min(pos_last + 1, k0 + chunk);
+  constexpr int kUnits = kRank / 8;                              // 16-byte units a row
+  for (int i = tid; i < kRowsPerBlock * 16 * kUnits; i += 256) {
+    const int rr = i / kUnits, un = i - rr * kUnits;
+    const int ri = rr / 16, hh = rr % 16;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (ri < n_rows && h0 + hh < heads)
+      v = *reinterpret_cast<const uint4*>(q + (static_cast<long long>(row0 + ri) * heads + h0 + hh) * kRank + un * 8);
+    *reinterpret_cast<uint4*>(Qs + rr * kPitch + un * 8) = v;
+  }
+  // this warp's row and its share of a tile's groups of 16 keys
+  const int ri = warp % kRowsPerBlock, stream = warp / kRowsPerBlock;
+  const bool active = ri < n_rows;
+  const int pos = active ? positions[row0 + ri] : -1;
+  const int first = (active && window > 0) ? max(0, pos - window + 1) : 0;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
   float O[kOut / 8][4];
 #pragma unroll
@@ -309,74 +339,78 @@ latent_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
       *reinterpret_cast<uint4*>(tile + j * kPitch + un * 8) = v;
     }
     __syncthreads();
-    const int kl = warp * 16;                                    // this warp's keys within the tile
-    if (t0 + kl >= k1) continue;
-    float S[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+    if (!active) continue;
+    for (int kl = stream * 16; kl < kMmaTileKeys; kl += kStreams * 16) {      // this warp's keys within the tile
+      if (t0 + kl >= k1 || t0 + kl > pos || t0 + kl + 15 < first) continue;
+      float S[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
 #pragma unroll
-    for (int ks = 0; ks < kRank / 16; ++ks) {
-      uint32_t a[4], b[4];
-      ldmatrix_x4(a, Qs + (lr + (mi & 1) * 8) * kPitch + ks * 16 + (mi >> 1) * 8);
-      ldmatrix_x4(b, tile + (kl + lr + (mi >> 1) * 8) * kPitch + ks * 16 + (mi & 1) * 8);
-      mma_bf16(S[0], a, b[0], b[1]);
-      mma_bf16(S[1], a, b[2], b[3]);
-    }
-    float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int kk = kl + nt * 8 + 2 * t4 + (c & 1);
-        const bool valid = t0 + kk < k1 && src_row[kk] >= 0;
-        S[nt][c] = valid ? S[nt][c] * scale : -INFINITY;
-        if (c < 2) mx0 = fmaxf(mx0, S[nt][c]); else mx1 = fmaxf(mx1, S[nt][c]);
+      for (int ks = 0; ks < kRank / 16; ++ks) {
+        uint32_t a[4], b[4];
+        ldmatrix_x4(a, Qs + (ri * 16 + lr + (mi & 1) * 8) * kPitch + ks * 16 + (mi >> 1) * 8);
+        ldmatrix_x4(b, tile + (kl + lr + (mi >> 1) * 8) * kPitch + ks * 16 + (mi & 1) * 8);
+        mma_bf16(S[0], a, b[0], b[1]);
+        mma_bf16(S[1], a, b[2], b[3]);
       }
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
-    const float corr0 = n0 == -INFINITY ? 1.0f : expf(m0 - n0), corr1 = n1 == -INFINITY ? 1.0f : expf(m1 - n1);
-    float sum0 = 0.0f, sum1 = 0.0f;
+      float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
+      for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const float nn = c < 2 ? n0 : n1;
-        const float pv = nn == -INFINITY ? 0.0f : expf(S[nt][c] - nn);
-        S[nt][c] = pv;
-        if (c < 2) sum0 += pv; else sum1 += pv;
-      }
-    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
-    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
-    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
-    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
-    l0 = fmaf(l0, corr0, sum0);
-    l1 = fmaf(l1, corr1, sum1);
-    m0 = n0;
-    m1 = n1;
-    uint32_t pa[4];
-    pa[0] = pack_bf16(S[0][0], S[0][1]);
-    pa[1] = pack_bf16(S[0][2], S[0][3]);
-    pa[2] = pack_bf16(S[1][0], S[1][1]);
-    pa[3] = pack_bf16(S[1][2], S[1][3]);
+        for (int c = 0; c < 4; ++c) {
+          const int kk = kl + nt * 8 + 2 * t4 + (c & 1);
+          const int key = t0 + kk;
+          const bool valid = key < k1 && key <= pos && key >= first && src_row[kk] >= 0;
+          S[nt][c] = valid ? S[nt][c] * scale : -INFINITY;
+          if (c < 2) mx0 = fmaxf(mx0, S[nt][c]); else mx1 = fmaxf(mx1, S[nt][c]);
+        }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float n0 = fmaxf(m0, mx0), n1 = fmaxf(m1, mx1);
+      const float corr0 = n0 == -INFINITY ? 1.0f : expf(m0 - n0), corr1 = n1 == -INFINITY ? 1.0f : expf(m1 - n1);
+      float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-    for (int nb = 0; nb < kOut / 16; ++nb) {
-      uint32_t b[4];
-      ldmatrix_x4_trans(b, tile + (kl + lr + (mi & 1) * 8) * kPitch + cbase + nb * 16 + (mi >> 1) * 8);
+      for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        float (&o)[4] = O[2 * nb + half];
-        o[0] *= corr0; o[1] *= corr0; o[2] *= corr1; o[3] *= corr1;
-        mma_bf16(o, pa, b[2 * half], b[2 * half + 1]);
+        for (int c = 0; c < 4; ++c) {
+          const float nn = c < 2 ? n0 : n1;
+          const float pv = nn == -INFINITY ? 0.0f : expf(S[nt][c] - nn);
+          S[nt][c] = pv;
+          if (c < 2) sum0 += pv; else sum1 += pv;
+        }
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+      sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+      sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+      l0 = fmaf(l0, corr0, sum0);
+      l1 = fmaf(l1, corr1, sum1);
+      m0 = n0;
+      m1 = n1;
+      uint32_t pa[4];
+      pa[0] = pack_bf16(S[0][0], S[0][1]);
+      pa[1] = pack_bf16(S[0][2], S[0][3]);
+      pa[2] = pack_bf16(S[1][0], S[1][1]);
+      pa[3] = pack_bf16(S[1][2], S[1][3]);
+#pragma unroll
+      for (int nb = 0; nb < kOut / 16; ++nb) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, tile + (kl + lr + (mi & 1) * 8) * kPitch + cbase + nb * 16 + (mi >> 1) * 8);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float (&o)[4] = O[2 * nb + half];
+          o[0] *= corr0; o[1] *= corr0; o[2] *= corr1; o[3] *= corr1;
+          mma_bf16(o, pa, b[2 * half], b[2 * half + 1]);
+        }
       }
     }
   }
-  const int parts = splits * 8;
+  if (!active) return;
+  const int parts = splits * kStreams;
 #pragma unroll
   for (int hr = 0; hr < 2; ++hr) {
     const int h = h0 + g + hr * 8;
     if (h >= heads) continue;
-    float* dst = partial + ((static_cast<long long>(row) * heads + h) * parts + split * 8 + warp) * (kRank + 2);
+    float* dst = partial + ((static_cast<long long>(row0 + ri) * heads + h) * parts + split * kStreams + stream) * (kRank + 2);
     if (t4 == 0 && cbase == 0) { dst[0] = hr ? m1 : m0; dst[1] = hr ? l1 : l0; }
 #pragma unroll
     for (int n = 0; n < kOut / 8; ++n) {
@@ -548,30 +582,37 @@ extern "C" int pih_latent_attention_split(int dtype, const void* q, const void* 
   return 0;
 }
 
-// The tensor-core kernel: bf16, rank 64, 128, 192, 256, 384 or 512.  partial: fp32 scratch, rows * heads * 8 * splits * (rank + 2).
+// The tensor-core kernel: bf16, rank 64, 128, 192, 256, 384 or 512.  rows_per_block 1 or 4 (4: blocks are row tiles
+// of a request, for steps of prompt portions).  partial: fp32 scratch, rows * heads * parts * (rank + 2) with
+// parts = splits * 8 / rows_per_block.
 extern "C" int pih_latent_attention_mma(const void* q, const void* gate, long long ldg, const void* sink, const void* cache,
                                         const void* block_table, int table_width, const void* request_of_row,
-                                        const void* positions, void* partial, void* out, int rows, int heads, int rank,
-                                        int page_size, int num_pages, float scale, int window, int splits, void* err,
-                                        void* stream) {
+                                        const void* positions, const void* cu_q, int requests, void* partial, void* out,
+                                        int rows, int heads, int rank, int page_size, int num_pages, float scale,
+                                        int window, int splits, int rows_per_block, void* err, void* stream) {
   if (rows <= 0) return 0;
   if ((rank != 64 && rank != 128 && rank != 192 && rank != 256 && rank != 384 && rank != 512) || splits < 1 ||
-      splits * 8 > kMergeParts || rows > 65535 * 32)
+      (rows_per_block != 1 && rows_per_block != 4) || splits * 8 / rows_per_block > kMergeParts || rows > 65535 * 32)
     return PIH_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const size_t smem = (16 + kMmaTileKeys) * static_cast<size_t>(rank + 8) * 2;
-  dim3 grid(rows, splits, (heads + 15) / 16 * (rank > 256 ? 2 : 1));
+  const size_t smem = (16 * rows_per_block + kMmaTileKeys) * static_cast<size_t>(rank + 8) * 2;
+  const unsigned blocks_x = rows_per_block == 1 ? rows : (rows + 3) / 4 + requests;
+  dim3 grid(blocks_x, splits, (heads + 15) / 16 * (rank > 256 ? 2 : 1));
   const long long items = static_cast<long long>(rows) * heads;
-#define PIH_LM(R, C)                                                                                                    \
+#define PIH_LM1(R, C, B)                                                                                               \
   do {                                                                                                                 \
     if (smem > 48 * 1024)                                                                                              \
-      cudaFuncSetAttribute(latent_attention_mma_kernel<R, C>, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
+      cudaFuncSetAttribute(latent_attention_mma_kernel<R, C, B>, cudaFuncAttributeMaxDynamicSharedMemorySize,          \
                            static_cast<int>(smem));                                                                    \
-    launch_kernel(latent_attention_mma_kernel<R, C>, grid, dim3(256), smem, s, static_cast<const bf16*>(q),               \
+    launch_kernel(latent_attention_mma_kernel<R, C, B>, grid, dim3(256), smem, s, static_cast<const bf16*>(q),         \
                   static_cast<const bf16*>(cache), static_cast<const int*>(block_table), table_width,                  \
                   static_cast<const int*>(request_of_row), static_cast<const int*>(positions),                         \
-                  static_cast<float*>(partial), heads, page_size, num_pages, scale, window, splits,                    \
-                  static_cast<uint32_t*>(err));                                                                        \
+                  static_cast<const int*>(cu_q), requests, static_cast<float*>(partial), heads, page_size, num_pages,  \
+                  scale, window, splits, static_cast<uint32_t*>(err));                                                 \
+  } while (0)
+#define PIH_LM(R, C)                                                                                                   \
+  do {                                                                                                                 \
+    if (rows_per_block == 1) PIH_LM1(R, C, 1); else PIH_LM1(R, C, 4);                                                  \
   } while (0)
   if (rank == 64) PIH_LM(64, 64);
   else if (rank == 128) PIH_LM(128, 128);
@@ -580,11 +621,12 @@ extern "C" int pih_latent_attention_mma(const void* q, const void* gate, long lo
   else if (rank == 384) PIH_LM(384, 192);
   else PIH_LM(512, 256);
 #undef PIH_LM
+#undef PIH_LM1
   PIH_LAUNCH_CHECK();
   launch_kernel(latent_merge_kernel<bf16>, dim3(static_cast<unsigned>(items)), dim3(rank >= 256 ? 256 : (rank + 31) / 32 * 32), 0, s,
                 static_cast<const float*>(partial), static_cast<const bf16*>(gate), ldg, static_cast<const float*>(sink),
-                static_cast<const int*>(request_of_row), static_cast<bf16*>(out), rows, heads, rank, splits * 8,
-                static_cast<uint32_t*>(err));
+                static_cast<const int*>(request_of_row), static_cast<bf16*>(out), rows, heads, rank,
+                splits * 8 / rows_per_block, static_cast<uint32_t*>(err));
   PIH_LAUNCH_CHECK();
   return 0;
 }

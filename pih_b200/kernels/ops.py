@@ -633,6 +633,7 @@ class CudaOps:
 
     latent_mma = True                      # bf16 attention over a latent of rank 64 ... 512: the tensor-core kernel ...
     latent_mma_min_rows = 0                # ... for steps of more rows than this
+    latent_mma_rows_above = 64             # ... with blocks of 4 rows of a request from this many rows on
     latent_split = True                    # bf16 attention over a latent: keys cut into parts (False: the in-order kernel)
     batched_library_min_rows = 128         # bf16 batched products of at least this many rows are the library's
 
@@ -728,13 +729,17 @@ class CudaOps:
         if q.dtype == torch.bfloat16 and self.latent_mma and rank in (64, 128, 192, 256, 384, 512) and T > self.latent_mma_min_rows:
             # tensor cores: the row's heads are the rows of the MMA, a tile of latents feeds every head's scores and sums;
             # a row's keys are cut into ``splits`` parts side by side, and each of a block's 8 warps is a part of its own
-            splits = max(1, min(16, (2 * 148) // max(1, T * (-(-heads // 16)))))
-            partial = torch.empty(T * heads * splits * 8 * (rank + 2), dtype=torch.float32, device=q.device)
+            # steps of many rows (prompt portions): a block is 4 consecutive rows of a request, which share a tile
+            per_block = 4 if T > self.latent_mma_rows_above else 1
+            blocks = (T if per_block == 1 else -(-T // 4) + step.num_requests) * (-(-heads // 16)) * (2 if rank > 256 else 1)
+            splits = max(1, min(16, (2 * 148) // max(1, blocks)))
+            parts = splits * 8 // per_block
+            partial = torch.empty(T * heads * parts * (rank + 2), dtype=torch.float32, device=q.device)
             rc = self.lib.pih_latent_attention_mma(
                 _ptr(q), _ptr(gate), c_ll(gate.stride(0) if gate is not None else 0), _ptr(sink), _ptr(cache),
-                _ptr(block_table), block_table.shape[1], _ptr(step.request_of_row), _ptr(step.positions), _ptr(partial),
-                _ptr(out), T, heads, rank, page_size, num_pages, c_float(scale), int(window), splits, self._err(),
-                self._stream())
+                _ptr(block_table), block_table.shape[1], _ptr(step.request_of_row), _ptr(step.positions), _ptr(step.cu_q),
+                step.num_requests, _ptr(partial), _ptr(out), T, heads, rank, page_size, num_pages, c_float(scale),
+                int(window), splits, per_block, self._err(), self._stream())
             if rc != -2:
                 self._check(rc, "latent_attention_mma")
                 self.launches += 1

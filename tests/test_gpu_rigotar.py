@@ -233,6 +233,51 @@ def test_latent_attention_finds_one_key_among_hundreds(needle, rank, dtype):
     assert float((got[0].double().cpu() - ref).abs().max()) < tol * float(ref.abs().max())
 
 
+@pytest.mark.parametrize("rank, heads", [(64, 5), (128, 18), (384, 3)])
+def test_latent_attention_portions_of_several_requests(rank, heads):
+    """Portions of three requests in one step — one deep in its context, one from its first token, one of five rows —
+    on the tensor-core kernel, whose blocks are four consecutive rows of ONE request: every row against the plain
+    softmax over its own request's latents up to its own position."""
+    from pih_b200.kernels import get_ops
+    ops = get_ops(torch.device(DEV))
+    g = torch.Generator().manual_seed(rank)
+    page = 16
+    starts, counts = [300, 0, 37], [70, 131, 5]
+    lats = [(torch.randn(st + n, rank, generator=g, dtype=F64) * 0.5).bfloat16() for st, n in zip(starts, counts)]
+    pages_of, next_page = [], 0
+    for lat in lats:
+        n_pages = -(-lat.shape[0] // page)
+        pages_of.append(list(range(next_page, next_page + n_pages))[::-1])
+        next_page += n_pages
+    cache = torch.zeros(next_page + 1, page, rank, dtype=torch.bfloat16, device=DEV)
+    width = max(len(p) for p in pages_of)
+    table = torch.full((3, width), -1, dtype=torch.int32)
+    for r, (lat, pages) in enumerate(zip(lats, pages_of)):
+        table[r, :len(pages)] = torch.tensor(pages, dtype=torch.int32)
+        for j in range(lat.shape[0]):
+            cache[pages[j // page], j % page] = lat[j].to(DEV)
+    T = sum(counts)
+    q = (torch.randn(T, heads, rank, generator=g, dtype=F64) * 0.6).bfloat16()
+    gate = (torch.randn(T, heads, generator=g, dtype=F64)).bfloat16()
+    sink = torch.randn(heads, generator=g, dtype=F64).float()
+    positions, request_of_row, cu = [], [], [0]
+    for r, (st, n) in enumerate(zip(starts, counts)):
+        positions += list(range(st, st + n))
+        request_of_row += [r] * n
+        cu.append(cu[-1] + n)
+    step = _step(positions, request_of_row, cu, [0, 1, 2])
+    assert T > ops.latent_mma_rows_above
+    got = ops.latent_attention(q.to(DEV).contiguous(), gate=gate.to(DEV), sink=sink.to(DEV), cache=cache,
+                               block_table=table.to(DEV), step=step, scale=0.3).double().cpu()
+    ops.check_errors()
+    worst = 0.0
+    for t in range(T):
+        r, p = request_of_row[t], positions[t]
+        ref = _plain_latent_rows(q[t].double(), lats[r][:p + 1].double(), sink.double(), gate[t].double(), 0.3)
+        worst = max(worst, float((got[t] - ref).abs().max()) / float(ref.abs().max()))
+    assert worst < 2e-2, worst
+
+
 def test_latent_attention_sink_and_window_edges():
     """The sink alone in the denominator (one key), no sink, and a window whose edge the standing-out key is just
     inside and just outside of."""
