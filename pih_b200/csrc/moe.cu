@@ -274,6 +274,47 @@ moe_gemv_kernel(const T* __restrict__ x, long long ldx, int row_div, const int* 
   }
 }
 
+// Few rows, many small matrices (a head's or a diagonal block's): out[t][b][n] = x[t][b] . W[b][n], a warp four output
+// columns, the matrix rows read with 16-byte loads.  K a multiple of 8 (bf16).
+template <typename T, typename TC>
+__global__ void __launch_bounds__(256)
+batched_gemv_kernel(const T* __restrict__ x, long long ldx, long long batch_x, const T* __restrict__ W, TC* __restrict__ out,
+                    int batches, int N, int K) {
+  constexpr int kVec = 16 / sizeof(T), kCols = 4;
+  extern __shared__ float xs[];
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int t = blockIdx.x / batches, b = blockIdx.x % batches;
+  const T* xr = x + t * ldx + b * batch_x;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float<T>(xr[k]);
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n0 = (blockIdx.y * (blockDim.x >> 5) + warp) * kCols;
+  if (n0 >= N) return;
+  const T* w = W + static_cast<long long>(b) * N * K;
+  float acc[kCols];
+#pragma unroll
+  for (int c = 0; c < kCols; ++c) acc[c] = 0.0f;
+  for (int k = lane * kVec; k < K; k += 32 * kVec) {
+    float xv[kVec];
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) xv[i] = xs[k + i];
+#pragma unroll
+    for (int c = 0; c < kCols; ++c) {
+      const int n = min(n0 + c, N - 1);
+      __align__(16) T wv[kVec];
+      *reinterpret_cast<uint4*>(wv) = *reinterpret_cast<const uint4*>(w + static_cast<long long>(n) * K + k);
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) acc[c] = fmaf(to_float<T>(wv[i]), xv[i], acc[c]);
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < kCols; ++c) {
+    const float v = warp_sum(acc[c]);
+    if (lane == 0 && n0 + c < N) out[(static_cast<long long>(blockIdx.x)) * N + n0 + c] = from_float<TC>(v);
+  }
+}
+
 template <typename T, typename TY>
 __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ pos_of,
                                    const float* __restrict__ weight_of, T* __restrict__ out, int rows, int hidden, int top) {
@@ -390,6 +431,26 @@ extern "C" int pih_moe_combine_bf16(const void* y, const void* ints, const void*
   launch_kernel(moe_combine_kernel<bf16, bf16>, dim3(rows), dim3(hidden >= 256 ? 256 : 128), 0, s,
                 static_cast<const bf16*>(y), pos_of, static_cast<const float*>(weight_of), static_cast<bf16*>(out), rows,
                 hidden, top);
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+// out[t][b] = x[t][b] . W[b]^T for few rows t in bf16: x element (t, b, k) at t * ldx + b * batch_x + k, W [batches, N, K],
+// out [rows, batches, N] contiguous, bf16 or fp32.
+extern "C" int pih_batched_gemv(int out_dtype, const void* x, long long ldx, long long batch_x, const void* W, void* out,
+                                int rows, int batches, int N, int K, void* stream) {
+  if (rows <= 0 || batches <= 0 || N <= 0) return 0;
+  if (K % 8 || K > 12288 || static_cast<long long>(rows) * batches > 65535 * 16) return PIH_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  dim3 grid(rows * batches, (N + 31) / 32);
+  if (out_dtype == PIH_BF16)
+    launch_kernel(batched_gemv_kernel<bf16, bf16>, grid, dim3(256), K * sizeof(float), s, static_cast<const bf16*>(x), ldx,
+                  batch_x, static_cast<const bf16*>(W), static_cast<bf16*>(out), batches, N, K);
+  else if (out_dtype == PIH_F32)
+    launch_kernel(batched_gemv_kernel<bf16, float>, grid, dim3(256), K * sizeof(float), s, static_cast<const bf16*>(x), ldx,
+                  batch_x, static_cast<const bf16*>(W), static_cast<float*>(out), batches, N, K);
+  else
+    return PIH_ERR_BAD_ARGUMENT;
   PIH_LAUNCH_CHECK();
   return 0;
 }

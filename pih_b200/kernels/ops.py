@@ -107,7 +107,7 @@ class CudaOps:
                      "pih_qk_attention_fused", "pih_gemm_tcgen05_pair", "pih_set_attention_side_by_side", "pih_set_skinny_rule",
                      "pih_gemm_simt_batched", "pih_embedding_stream", "pih_rmsnorm_stream", "pih_causal_conv",
                      "pih_gated_delta_rule", "pih_gated_rmsnorm", "pih_rglru_scan", "pih_latent_write",
-                     "pih_latent_attention_generic", "pih_moe_route", "pih_moe_experts", "pih_moe_combine_bf16", "pih_latent_attention_split", "pih_latent_attention_splits", "pih_latent_attention_mma"):
+                     "pih_latent_attention_generic", "pih_moe_route", "pih_moe_experts", "pih_moe_combine_bf16", "pih_latent_attention_split", "pih_latent_attention_splits", "pih_latent_attention_mma", "pih_batched_gemv"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
         lib.pih_top_logprobs_scratch_words.restype = c_ll
@@ -625,6 +625,13 @@ class CudaOps:
             # many rows in bf16: the library's batched product (32-bit accumulation), as the single products of many rows
             return torch.bmm(x.transpose(0, 1), w.transpose(1, 2)).transpose(0, 1).contiguous()
         out = torch.empty(T, B, N, dtype=out_dtype, device=x.device)
+        if x.dtype == torch.bfloat16 and T <= self.skinny_max_rows and K % 8 == 0:
+            # few rows in bf16: a warp an output column, the small matrices' rows streamed once
+            rc = self.lib.pih_batched_gemv(_DT[out_dtype], _ptr(x), c_ll(x.stride(0)), c_ll(x.stride(1)), _ptr(w), _ptr(out),
+                                           T, B, N, K, self._stream())
+            if rc != -2:
+                self._check(rc, "batched_gemv")
+                return out
         rc = self.lib.pih_gemm_simt_batched(_DT[x.dtype], _DT[out_dtype], _ptr(x), _ptr(w), _ptr(out), T, N, K,
                                             c_ll(x.stride(0)), c_ll(K), c_ll(B * N), B, c_ll(x.stride(1)), c_ll(N * K),
                                             c_ll(N), self._stream())
