@@ -414,3 +414,53 @@ def test_greedy_generation_through_the_engine(dirs, cuda_graphs):
     engine.rt.ops.check_errors()
     for r, expect in zip(results, want):
         assert r["token_ids"] == expect
+
+
+def test_command_lines(dirs, tmp_path):
+    """bin/pih-worker makes a random Rigotar model from a configuration file and generates from it; bin/trace_run
+    replays a trace on it; both agree with the plain implementation."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+    from conftest import ROOT
+    worker = [sys.executable, os.path.join(ROOT, "bin", "pih-worker")]
+    cfg_file = tmp_path / "config.json"
+    cfg_file.write_text(json.dumps(rm.R2))
+    folder = str(tmp_path / "made")
+    proc = subprocess.run(worker + ["--random-model", folder, "--config", str(cfg_file), "--seed", "4", "--sigma", "0.15"],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    prompt = [5, 17, 3, 200, 9]
+    proc = subprocess.run(worker + ["--model", folder, "--generate-tokens", ",".join(map(str, prompt)), "--max-tokens", "7",
+                                    "--dtype", "float32", "--ignore-eos"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    res = json.loads(proc.stdout.strip().splitlines()[-1])
+    cfg, w = rm.load_plain(folder)
+    toks = list(prompt)
+    for _ in range(7):
+        toks.append(int(plain.forward(cfg, w, toks)[-1].argmax()))
+    assert res["token_ids"] == toks[len(prompt):]
+
+    requests = traces.make_requests(rm.R2["vocab"], [40, 9, 23], seed=6)
+    steps = traces.mixed(requests, seed=1, max_live=3)
+    for s_ in steps:
+        for e in s_["entries"]:
+            e["want"] = e["want"][-1:]                              # the last place of every portion
+    out_dir = str(tmp_path / "out")
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out", out_dir,
+           "--max-tokens", str(traces.peak_tokens(steps))]
+    proc = subprocess.run(cmd, input="\n".join(json.dumps(s_) for s_ in steps) + "\n", capture_output=True, text=True,
+                          timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s_['step']}" for s_ in steps]
+    truth = rm.plain_logits(folder, requests)
+    at = {rid: 0 for rid in requests}
+    for s_ in steps:
+        got = np.fromfile(os.path.join(out_dir, f"{s_['step']}.f32"), dtype="<f4").reshape(-1, rm.R2["vocab"])
+        for j, e in enumerate(s_["entries"]):
+            at[e["id"]] += len(e["tokens"])
+            ref = truth[e["id"]][at[e["id"]] - 1].numpy()
+            assert np.abs(got[j] - ref).max() < 1e-4 * max(1.0, np.abs(ref).max()), (s_["step"], e["id"])
