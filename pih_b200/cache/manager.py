@@ -238,8 +238,9 @@ class CacheManager:
                 total[g] += c
         return all(total[g] <= self.groups[g].pool.num_free for g in range(len(self.groups)))
 
-    def append(self, rid: Hashable, n_new: int) -> None:
-        """Make room for the next ``n_new`` tokens of ``rid`` in every group, or in none."""
+    def append(self, rid: Hashable, n_new: int, snapshot: bool = True) -> None:
+        """Make room for the next ``n_new`` tokens of ``rid`` in every group, or in none.  ``snapshot`` False: the
+        caller keeps the copy of the state slots for all requests of the step at once (``snapshot_states``)."""
         if n_new < 1:
             raise ValueError("append needs at least one token")
         rc = self.requests[rid]
@@ -250,10 +251,28 @@ class CacheManager:
                                  f"{self.groups[g].pool.num_free} free")
         for g, c in enumerate(need):
             rc.pages[g].extend(self.groups[g].pool.allocate(c, rid))
-        if rc.pending == 0 and self.state_tensors:
+        if snapshot and rc.pending == 0 and self.state_tensors:
             # the state as it is before this step (copies queued on the current stream, ahead of the step)
             rc.state_pending = {e: t[rc.slot].clone() for e, t in self.state_tensors.items()}
         rc.pending += n_new
+
+    def snapshot_states(self, rids: Sequence[Hashable], slots: torch.Tensor) -> None:
+        """The state slots of the step's requests as they are before the step, for ``rollback``: ONE gather a state
+        tensor for all requests (``slots``: their slots in the order of ``rids``, int32 on the device — the step's own
+        array), instead of a copy a request and tensor, which for eight requests and eight layers with a state was
+        64 launches a step.  Queued on the current stream, ahead of the step."""
+        if not self.state_tensors:
+            return
+        reqs = [self.requests[r] for r in rids]
+        if any(rc.state_pending is not None for rc in reqs):           # (a second append before a commit: one by one)
+            for rc in reqs:
+                if rc.state_pending is None:
+                    rc.state_pending = {e: t[rc.slot].clone() for e, t in self.state_tensors.items()}
+            return
+        index = slots[:len(reqs)]
+        saved = {e: t.index_select(0, index) for e, t in self.state_tensors.items()}
+        for i, rc in enumerate(reqs):
+            rc.state_pending = {e: rows[i] for e, rows in saved.items()}
 
     def rollback(self, rid: Hashable, unconfirmed: bool = False) -> None:
         """Undo appends that were not committed (the step did not run): their pages go back, and the state

@@ -21,7 +21,8 @@ constexpr int kMoeTile = 64;
 // One warp a row.  A logit that is not a number counts as the smallest; ties go to the smaller index.
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, int rows, int experts, int top, int* __restrict__ expert_of,
-                 float* __restrict__ weight_of, int* __restrict__ rank_of, int* __restrict__ counts) {
+                 float* __restrict__ weight_of, int* __restrict__ rank_of, int* __restrict__ counts,
+                 int* __restrict__ pos_of) {
   wait_for_prior_kernels();
   launch_dependents();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -61,7 +62,9 @@ moe_route_kernel(const float* __restrict__ logits, int rows, int experts, int to
     if (lane == 0) {
       expert_of[static_cast<long long>(row) * top + k] = best_i;
       weight_of[static_cast<long long>(row) * top + k] = e_k;
-      rank_of[static_cast<long long>(row) * top + k] = atomicAdd(&counts[best_i], 1);
+      // grouped by expert: the row's place among the expert's rows; not grouped (counts null): a slot stays where it is
+      if (counts != nullptr) rank_of[static_cast<long long>(row) * top + k] = atomicAdd(&counts[best_i], 1);
+      else pos_of[static_cast<long long>(row) * top + k] = row * top + k;
     }
   }
   __syncwarp();
@@ -342,7 +345,9 @@ extern "C" long long pih_moe_route_words(int rows, int experts, int top) {
   return 4LL * rows * top + experts + 2LL * experts + 2;
 }
 
-extern "C" int pih_moe_route(const void* logits, int rows, int experts, int top, void* ints, void* weight_of, void* stream) {
+// grouped 0: only the choice and the weights (for the kernels that take every slot on its own; ints need no zeroing)
+extern "C" int pih_moe_route(const void* logits, int rows, int experts, int top, void* ints, void* weight_of, int grouped,
+                             void* stream) {
   if (rows <= 0) return 0;
   if (experts < 1 || experts > 1024 || top < 1 || top > experts) return PIH_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -354,8 +359,9 @@ extern "C" int pih_moe_route(const void* logits, int rows, int experts, int top,
   int* counts = row_of + slots;
   int* plan = counts + experts;
   launch_kernel(moe_route_kernel, dim3((rows + 3) / 4), dim3(128), 0, s, static_cast<const float*>(logits), rows, experts,
-                top, expert_of, static_cast<float*>(weight_of), rank_of, counts);
+                top, expert_of, static_cast<float*>(weight_of), rank_of, grouped ? counts : static_cast<int*>(nullptr), pos_of);
   PIH_LAUNCH_CHECK();
+  if (!grouped) return 0;
   launch_kernel(moe_plan_kernel, dim3(1), dim3(32), 0, s, static_cast<const int*>(counts), experts, plan);
   PIH_LAUNCH_CHECK();
   launch_kernel(moe_scatter_kernel, dim3(static_cast<unsigned>((slots + 255) / 256)), dim3(256), 0, s,

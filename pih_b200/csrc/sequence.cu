@@ -497,6 +497,7 @@ rglru_chain_kernel(const float4* __restrict__ coef, T* __restrict__ out, long lo
   state[slot * state_stride + c] = S;
 }
 
+
 }  // namespace pih
 
 using namespace pih;

@@ -125,13 +125,19 @@ class ModelRunner:
         done = []
         try:
             for e in entries:
-                self.cache.append(e.rid, len(e.tokens))
+                self.cache.append(e.rid, len(e.tokens), snapshot=False)
                 done.append(e.rid)
         except OutOfPages:
             for rid in done:
                 self.cache.rollback(rid)
             raise
-        return self.builder.build(entries, self.cache)
+        return self._snapshot(entries, self.builder.build(entries, self.cache))
+
+    def _snapshot(self, entries, batch: StepBatch) -> StepBatch:
+        """Keep the requests' state slots as they are before the step (one gather a state tensor, by the step's own
+        array of slots on the device)."""
+        self.cache.snapshot_states([e.rid for e in entries], batch.state_slots)
+        return batch
 
     def run(self, batch: StepBatch) -> Optional[torch.Tensor]:
         caches = [self.cache.view(i, batch.block_tables, batch.slot_mappings)
@@ -267,7 +273,7 @@ class ModelRunner:
         done = []
         try:
             for e in entries:
-                self.cache.append(e.rid, len(e.tokens))
+                self.cache.append(e.rid, len(e.tokens), snapshot=False)
                 done.append(e.rid)
         except OutOfPages:
             for rid in done:
@@ -294,6 +300,7 @@ class ModelRunner:
                 else:
                     batch = self.builder.build(entries, self.cache, width=width, pad=pad)
                     batch.attention_plans = self._plans(kind, width * self.cache.page_size)
+                self._snapshot(entries, batch)
                 batch.padded = True                               # (a shape that comes again, padded or not)
                 self._feed(batch, token_feed)
                 logits = self.run(batch)
@@ -302,6 +309,7 @@ class ModelRunner:
                 logits = self._capture(entries, key, width, token_feed)
             else:
                 batch = self.builder.build(entries, self.cache, width=width, device_buffer=state["buffer"], pad=pad)
+                self._snapshot(entries, batch)
                 self._feed(batch, token_feed)
                 if key[0] != "decode":
                     self._graphs[key] = self._graphs.pop(key)     # most recently used last
@@ -333,6 +341,7 @@ class ModelRunner:
             T, B, S = pad
         buffer = torch.empty(self.builder.buffer_size(T, B, S, G, width), dtype=torch.int32, device=self.device)
         batch = self.builder.build(entries, self.cache, width=width, device_buffer=buffer, pad=pad)
+        self._snapshot(entries, batch)
         batch.padded = True
         self._feed(batch, token_feed)
         ops = self.model.rt.ops

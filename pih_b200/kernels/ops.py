@@ -792,15 +792,18 @@ class CudaOps:
         assert logits.dtype == torch.float32 and logits.is_contiguous() and logits.shape == (T, experts)
         assert x.stride(1) == 1 and w_gate_up.is_contiguous() and w_down.is_contiguous()
         slots = T * top
-        words = self.lib.pih_moe_route_words(T, experts, top)
-        ints = torch.zeros(int(words), dtype=torch.int32, device=x.device)
-        weight_of = torch.empty(slots, dtype=torch.float32, device=x.device)
-        rc = self.lib.pih_moe_route(_ptr(logits), T, experts, top, _ptr(ints), _ptr(weight_of), self._stream())
-        self._check(rc, "moe_route")
-        self.launches += 2
-        out = torch.empty(T, hidden, dtype=x.dtype, device=x.device)
         bf16 = x.dtype == torch.bfloat16
-        if (bf16 and slots >= self.moe_library_min_slots and hidden % 8 == 0 and ff % 8 == 0
+        vec = 8 if bf16 else 4
+        few = bf16 and slots <= self.moe_few_slots and hidden % vec == 0 and ff % vec == 0 and max(hidden, ff) <= 12288
+        words = self.lib.pih_moe_route_words(T, experts, top)
+        # (few rows: every slot is taken on its own, nothing is grouped or counted)
+        ints = (torch.empty if few else torch.zeros)(int(words), dtype=torch.int32, device=x.device)
+        weight_of = torch.empty(slots, dtype=torch.float32, device=x.device)
+        rc = self.lib.pih_moe_route(_ptr(logits), T, experts, top, _ptr(ints), _ptr(weight_of), 0 if few else 1, self._stream())
+        self._check(rc, "moe_route")
+        self.launches += 0 if few else 2
+        out = torch.empty(T, hidden, dtype=x.dtype, device=x.device)
+        if (bf16 and not few and slots >= self.moe_library_min_slots and hidden % 8 == 0 and ff % 8 == 0
                 and hasattr(torch, "_grouped_mm")):
             row_of = ints[3 * slots:4 * slots]
             ends = ints[4 * slots + experts + 1:4 * slots + 2 * experts + 1]          # where each expert's rows end
@@ -814,14 +817,9 @@ class CudaOps:
             return out
         act = torch.empty(slots, ff, dtype=x.dtype, device=x.device)
         y = torch.empty(slots, hidden, dtype=torch.float32, device=x.device)
-        few = 1 if (bf16 and slots <= self.moe_few_slots) else 0
         rc = self.lib.pih_moe_experts(_DT[x.dtype], _ptr(x), c_ll(x.stride(0)), _ptr(w_gate_up), _ptr(w_down), _ptr(act),
-                                      _ptr(y), _ptr(out), _ptr(ints), _ptr(weight_of), T, experts, top, hidden, ff, few,
-                                      self._stream())
-        if rc == -2 and few:
-            rc = self.lib.pih_moe_experts(_DT[x.dtype], _ptr(x), c_ll(x.stride(0)), _ptr(w_gate_up), _ptr(w_down),
-                                          _ptr(act), _ptr(y), _ptr(out), _ptr(ints), _ptr(weight_of), T, experts, top,
-                                          hidden, ff, 0, self._stream())
+                                      _ptr(y), _ptr(out), _ptr(ints), _ptr(weight_of), T, experts, top, hidden, ff,
+                                      1 if few else 0, self._stream())
         self._check(rc, "moe_experts")
         self.launches += 2
         return out
