@@ -433,7 +433,7 @@ gated_rmsnorm_kernel(const float* __restrict__ o, const T* __restrict__ gate, lo
 // the convolution's output u and the other branch y_pre [rows, ldy] before its bias and GELU, the three numbers that
 // the recurrence needs of a token: coef[row][c] = (a - 1, sqrt(1 - a^2) * i * u, gelu(y), 0).  rglru_chain (a thread a
 // (request, channel)): S <- S + (a - 1) S + b, out = S * y over the request's rows in order, eight tokens' numbers in
-// flight ahead of the chain.
+// flight ahead of the chain (sixteen tokens fetched while sixteen are computed).
 template <typename T>
 __global__ void __launch_bounds__(256)
 rglru_gates_kernel(const T* __restrict__ u, long long ldu, const float* __restrict__ gates, const T* __restrict__ y_pre,
@@ -471,7 +471,7 @@ rglru_chain_kernel(const float4* __restrict__ coef, T* __restrict__ out, long lo
   const int slot = state_slots[r];
   if (hi <= lo || slot < 0 || c >= width) return;
   float S = state[slot * state_stride + c];
-  constexpr int kAhead = 8;
+  constexpr int kAhead = 16;
   float4 cur[kAhead], nxt[kAhead];
   auto fetch = [&](float4 (&f)[kAhead], int t0) {
 #pragma unroll
@@ -488,7 +488,7 @@ rglru_chain_kernel(const float4* __restrict__ coef, T* __restrict__ out, long lo
     }
   };
   fetch(cur, lo);
-  for (int t0 = lo; t0 < hi; t0 += 2 * kAhead) {           // the next eight tokens' numbers are under way during the chain
+  for (int t0 = lo; t0 < hi; t0 += 2 * kAhead) {           // the next sixteen tokens' numbers are under way during the chain
     fetch(nxt, t0 + kAhead);
     chain(cur, t0);
     fetch(cur, t0 + 2 * kAhead);

@@ -346,6 +346,61 @@ def test_delta_rule_recalls_a_value_written_long_ago():
         assert float((S.transpose(1, 2) @ keys[i] - v[last]).abs().max()) < 1e-4
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dim, vdim", [(16, 24), (32, 32), (48, 40), (64, 70), (128, 128), (256, 64), (40, 8)])
+def test_delta_rule_kernels_of_every_key_size(dim, vdim, dtype):
+    """The register kernel's instances (key sizes 16 to 256) and the shared-memory kernel (the other sizes), value sizes
+    that are no multiple of a block's 32 columns, two requests of unequal length in two steps, against plain loops."""
+    from pih_b200.kernels import get_ops
+    ops = get_ops(torch.device(DEV))
+    g = torch.Generator().manual_seed(dim + vdim)
+    heads, kv_heads = 4, 2
+    lens = [37, 9]
+    T = sum(lens)
+    QK, VS = kv_heads * dim, heads * vdim
+    qkv = (torch.randn(T, 2 * QK + VS, generator=g) * 0.7).to(dtype)
+    ba = torch.randn(T, 2 * heads, generator=g).to(dtype)
+    decay_log = torch.randn(heads, generator=g) * 0.5 - 1.0
+    decay_bias = torch.randn(heads, generator=g) * 0.5
+    state = torch.zeros(3, heads * dim * vdim + 5, dtype=torch.float32, device=DEV)
+    kw = dict(decay_log=decay_log.to(DEV), decay_bias=decay_bias.to(DEV), state=state, heads=heads, kv_heads=kv_heads,
+              key_dim=dim, value_dim=vdim, unit_eps=1e-6, q_scale=dim ** -0.5)
+    # step 1: the first 20 rows of request 0 and all of request 1; step 2: the rest of request 0
+    rows1 = list(range(20)) + list(range(lens[0], T))
+    rows2 = list(range(20, lens[0]))
+    sel1, sel2 = torch.tensor(rows1), torch.tensor(rows2)
+    out1 = ops.gated_delta_rule(qkv[sel1].to(DEV).contiguous(), ba[sel1].to(DEV).contiguous(),
+                                step=_step([0] * len(rows1), [0] * len(rows1), [0, 20, len(rows1)], [2, 0]), **kw)
+    out2 = ops.gated_delta_rule(qkv[sel2].to(DEV).contiguous(), ba[sel2].to(DEV).contiguous(),
+                                step=_step([0] * len(rows2), [0] * len(rows2), [0, len(rows2)], [2]), **kw)
+    ops.check_errors()
+    got = torch.zeros(T, heads, vdim, dtype=F64)
+    got[sel1] = out1.double().cpu()
+    got[sel2] = out2.double().cpu()
+    x = qkv.double()
+    q = x[:, :QK].view(T, kv_heads, dim)
+    k = x[:, QK:2 * QK].view(T, kv_heads, dim)
+    v = x[:, 2 * QK:].view(T, heads, vdim)
+    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dim ** -0.5
+    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    beta = torch.sigmoid(ba.double()[:, :heads])
+    dec = torch.exp(-torch.exp(decay_log.double()) * plain.softplus(ba.double()[:, heads:] + decay_bias.double()))
+    ref = torch.zeros(T, heads, vdim, dtype=F64)
+    start = 0
+    for n in lens:
+        for h in range(heads):
+            S = torch.zeros(dim, vdim, dtype=F64)
+            for t in range(start, start + n):
+                kk, qq = k[t, h // 2], q[t, h // 2]
+                S = dec[t, h] * S
+                S = S + torch.outer(kk, beta[t, h] * (v[t, h] - S.T @ kk))
+                ref[t, h] = S.T @ qq
+        start += n
+    tol = 2e-5 if dtype == torch.float32 else 1e-4            # (the inputs are what the kernel read; only the arithmetic differs)
+    assert float((got - ref).abs().max()) < tol * max(1.0, float(ref.abs().max()))
+    assert float(state[1].abs().max()) == 0.0 and float(state[:, -5:].abs().max()) == 0.0      # nothing beyond the matrices
+
+
 def test_rglru_keeps_a_state_over_a_thousand_tokens():
     """A channel with a decay next to one: an input at token 0 is still there 1500 tokens later, fed in portions and
     token by token, where a decay rounded to 32-bit before it multiplies would have lost a few percent of it."""
