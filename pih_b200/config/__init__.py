@@ -1,12 +1,15 @@
 """Typed configurations and the architecture registry."""
 from .registry import (config_class_for, config_from_dict, load_config, register_architecture,
                        registered_architectures)
-from .specs import (AttentionSpec, BlockSpec, GatedDeltaSpec, LatentAttentionSpec, ModelSpec, MoESpec, NormSpec,
-                    RGLRUSpec, RopeSpec, ScalarNormSpec, ScheduleEntry, SwiGLUSpec)
+from .specs import (AttentionSpec, BiasedMLPSpec, BlockSpec, ComputedRopeSpec, DiffAttentionSpec, GatedDeltaSpec,
+                    LatentAttentionSpec, ModelSpec, MoESpec, NormSpec, RetentionSpec, RGLRUSpec, RopeSpec, ScalarNormSpec,
+                    ScheduleEntry, ScoredMoESpec, SwiGLUSpec)
 from .qwen3 import Qwen3Config
 from .rigotar import RigotarConfig
+from .tuganex import TuganexConfig
 
 __all__ = ["config_class_for", "config_from_dict", "load_config", "register_architecture",
            "registered_architectures", "AttentionSpec", "BlockSpec", "ModelSpec", "NormSpec",
            "RopeSpec", "ScheduleEntry", "SwiGLUSpec", "Qwen3Config", "GatedDeltaSpec", "LatentAttentionSpec", "MoESpec",
-           "RGLRUSpec", "ScalarNormSpec", "RigotarConfig"]
+           "RGLRUSpec", "ScalarNormSpec", "RigotarConfig", "BiasedMLPSpec", "ComputedRopeSpec", "DiffAttentionSpec",
+           "RetentionSpec", "ScoredMoESpec", "TuganexConfig"]

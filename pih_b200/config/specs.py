@@ -26,6 +26,7 @@ class NormSpec:
     width: int
     eps: float
     kind: str = "rmsnorm"
+    weight_name: str = "weight"       # behind the norm's prefix ("": the prefix itself names the tensor)
 
 
 @dataclass(frozen=True)
@@ -157,9 +158,126 @@ class MoESpec:
 
 
 @dataclass(frozen=True)
+class ComputedRopeSpec:
+    """Rotate-half rotary encoding whose angles the kernels compute from the position (32-bit ``position * f_i`` with
+    ``f_i = theta^(-2i/rotary_dim)``): no table, so no longest context has to be known."""
+    head_dim: int
+    rotary_dim: int
+    theta: float
+    kind: str = "rope_computed"
+
+
+@dataclass(frozen=True)
+class RetentionSpec:
+    """Retention: linear attention with one fixed decay a head and neither softmax nor denominator.  Per head a
+    matrix state ``S [key_dim, value_dim]``: ``S <- decay * S + k v^T``, read-out ``S^T q``.  q and k are rotated
+    (``position``), k is scaled by ``key_scale`` after the rotation; the read-out of a head is divided by its root
+    mean square (``norm_eps``, no weight) and multiplied by ``silu`` of a gate projection."""
+    hidden: int
+    heads: int
+    key_dim: int
+    value_dim: int
+    decays: Sequence[float]           # one a head, in (0, 1]
+    key_scale: float
+    norm_eps: float
+    position: Optional[object]
+    kind: str = "retention"
+    names: Mapping[str, str] = _names(q="mix.q", k="mix.k", v="mix.v", gate="mix.g", o="mix.o")
+
+    @property
+    def qk_size(self) -> int:
+        return self.heads * self.key_dim
+
+    @property
+    def v_size(self) -> int:
+        return self.heads * self.value_dim
+
+
+@dataclass(frozen=True)
+class DiffAttentionSpec:
+    """Differential attention: every head has two maps, each a causal softmax attention of its own (queries and keys
+    of ``key_dim``, laid out head by head as [map 1 | map 2]) over the SAME values (``value_dim``); the head's output
+    is ``a1 - lambda * a2`` with one ``lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + lambda_init`` a layer, divided by
+    its root mean square over ``value_dim`` (``norm_eps``, no weight) and multiplied by ``out_scale``.  q and k pass a
+    per-map RMS norm (``qk_norm_eps``; None: no norm) and the rotation ``position``.  ``kv_heads`` key/value heads
+    serve groups of query heads.  ``own_kv`` False: the mixer has no key/value tensors and reads another entry's
+    cache."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    key_dim: int
+    value_dim: int
+    scale: float
+    lambda_init: float
+    out_scale: float
+    norm_eps: float
+    qk_norm_eps: Optional[float]
+    position: Optional[object]
+    window: Optional[int] = None
+    own_kv: bool = True
+    kind: str = "diff_attention"
+    names: Mapping[str, str] = _names(q="mix.q", k="mix.k", v="mix.v", o="mix.o", q_norm="mix.q.norm",
+                                      k_norm="mix.k.norm", lq1="mix.lq1", lk1="mix.lk1", lq2="mix.lq2", lk2="mix.lk2")
+
+    @property
+    def q_size(self) -> int:
+        return self.heads * 2 * self.key_dim
+
+    @property
+    def k_size(self) -> int:
+        return self.kv_heads * 2 * self.key_dim
+
+    @property
+    def v_size(self) -> int:
+        return self.kv_heads * self.value_dim
+
+
+@dataclass(frozen=True)
+class BiasedMLPSpec:
+    """Two-matrix feed-forward with biases: ``W_down act(W_up x + b_up) + b_down``.  ``activation`` "xielu": for
+    z > 0 ``softplus(p) z^2 + z / 2``, else ``(1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2`` with the two learned
+    numbers (p, q) of the tensor ``act``."""
+    hidden: int
+    intermediate: int
+    activation: str = "xielu"
+    kind: str = "biased_mlp"
+    names: Mapping[str, str] = _names(up="mlp.up", up_bias="mlp.up.b", down="mlp.down", down_bias="mlp.down.b",
+                                      act="mlp.act")
+
+
+@dataclass(frozen=True)
+class ScoredMoESpec:
+    """Mixture of gated feed-forward experts whose router scores every output with a softmax over ALL of them:
+    ``experts`` real experts and behind them ``identity`` experts without tensors whose output is the input itself.
+    The choice goes by ``score + correction`` (a learned vector), restricted to the ``groups_keep`` best of
+    ``groups`` equal groups of neighbouring outputs (a group's score: its largest choice score); the ``top`` chosen
+    outputs weigh with their scores, as they are (``renormalize`` False) or divided by their sum.  ``shared``: a
+    gated feed-forward that runs for every row and is added, multiplied by ``sigmoid`` of a one-row projection."""
+    hidden: int
+    experts: int
+    identity: int
+    top: int
+    intermediate: int
+    groups: int = 1
+    groups_keep: int = 1
+    renormalize: bool = False
+    shared: Optional[SwiGLUSpec] = None
+    activation: str = "silu"
+    kind: str = "scored_moe"
+    names: Mapping[str, str] = _names(router="mlp.router", correction="mlp.correction", expert="mlp.e{}.", gate="gate",
+                                      up="up", down="down", shared_gate="mlp.shared.sg")
+
+    @property
+    def outputs(self) -> int:
+        return self.experts + self.identity
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: ``h += mixer(norm_in(h)); h += ffn(norm_post(h))`` for
-    ``arrangement == "prenorm"``; ``ffn`` and ``norm_post`` None: the layer has
+    ``arrangement == "prenorm"``; ``h += norm_in(mixer(h)); h += norm_post(ffn(h))``
+    for ``arrangement == "outnorm"`` (the norms sit on the sub-layers' outputs,
+    the sub-layers read the stream itself); ``ffn`` and ``norm_post`` None: the layer has
     no feed-forward.  ``prefix`` is the layer's tensor-name prefix in the
     weight files."""
     prefix: str

@@ -73,6 +73,108 @@ moe_route_kernel(const float* __restrict__ logits, int rows, int experts, int to
   }
 }
 
+// Routing by scores over ALL outputs: s = softmax(logits); the choice goes by s + correction, among the outputs of the
+// ``keep`` best of ``groups`` equal groups of neighbours (a group's score: its largest choice score; the others count
+// as minus infinity); the ``top`` largest are chosen (ties: the smaller index) and weigh with their s, divided by the
+// chosen ones' sum only with ``renormalize``.  One warp a row; ``flags``: [warps][groups] ints of shared memory.
+__global__ void __launch_bounds__(128)
+moe_route_scored_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ correction, int rows,
+                        int experts, int top, int groups, int keep, int renormalize, int* __restrict__ expert_of,
+                        float* __restrict__ weight_of, int* __restrict__ rank_of, int* __restrict__ counts,
+                        int* __restrict__ pos_of) {
+  extern __shared__ float route_smem[];
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int kPer = 32;                                       // experts <= 1024
+  float sc[kPer], ch[kPer];
+  uint32_t taken = 0;
+  float mx = -INFINITY;
+#pragma unroll
+  for (int e = 0; e < kPer; ++e) {
+    const int i = lane + 32 * e;
+    float a = (e * 32 < experts && i < experts) ? logits[row * ld + i] : -INFINITY;
+    sc[e] = (a == a) ? a : -INFINITY;
+    mx = fmaxf(mx, sc[e]);
+  }
+  mx = warp_max(mx);
+  float sum = 0.0f;
+#pragma unroll
+  for (int e = 0; e < kPer; ++e) {
+    sc[e] = (e * 32 < experts && sc[e] != -INFINITY) ? expf(sc[e] - mx) : 0.0f;
+    sum += sc[e];
+  }
+  sum = warp_sum(sum);
+  const float inv = 1.0f / sum;
+#pragma unroll
+  for (int e = 0; e < kPer; ++e) {
+    const int i = lane + 32 * e;
+    sc[e] *= inv;
+    ch[e] = (e * 32 < experts && i < experts) ? sc[e] + (correction != nullptr ? correction[i] : 0.0f) : -INFINITY;
+  }
+  if (groups > 1) {
+    float* score = route_smem + warp * 2 * groups;               // a group's score, then whether it is kept
+    int* kept = reinterpret_cast<int*>(score + groups);
+    const int size = experts / groups;
+    for (int g = 0; g < groups; ++g) {
+      float best = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < kPer; ++e) {
+        const int i = lane + 32 * e;
+        if (e * 32 < experts && i < experts && i / size == g) best = fmaxf(best, ch[e]);
+      }
+      best = warp_max(best);
+      if (lane == 0) score[g] = best;
+    }
+    __syncwarp();
+    for (int g = lane; g < groups; g += 32) {
+      int ahead = 0;
+      for (int o = 0; o < groups; ++o) ahead += (score[o] > score[g] || (score[o] == score[g] && o < g)) ? 1 : 0;
+      kept[g] = ahead < keep ? 1 : 0;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int e = 0; e < kPer; ++e) {
+      const int i = lane + 32 * e;
+      if (e * 32 < experts && i < experts && !kept[i / size]) ch[e] = -INFINITY;
+    }
+  }
+  float chosen_sum = 0.0f;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY, best_s = 0.0f;
+    int best_i = 0x7fffffff;
+#pragma unroll
+    for (int e = 0; e < kPer; ++e) {
+      const int i = lane + 32 * e;
+      if (e * 32 < experts && i < experts && !((taken >> e) & 1u) && (ch[e] > best || best_i == 0x7fffffff)) {
+        best = ch[e];
+        best_s = sc[e];
+        best_i = i;
+      }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, d);
+      const float os = __shfl_xor_sync(0xffffffffu, best_s, d);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, d);
+      if (oi != 0x7fffffff && (best_i == 0x7fffffff || ob > best || (ob == best && oi < best_i))) { best = ob; best_s = os; best_i = oi; }
+    }
+    if ((best_i & 31) == lane) taken |= 1u << (best_i >> 5);
+    chosen_sum += best_s;
+    if (lane == 0) {
+      expert_of[static_cast<long long>(row) * top + k] = best_i;
+      weight_of[static_cast<long long>(row) * top + k] = best_s;
+      if (counts != nullptr) rank_of[static_cast<long long>(row) * top + k] = atomicAdd(&counts[best_i], 1);
+      else pos_of[static_cast<long long>(row) * top + k] = row * top + k;
+    }
+  }
+  __syncwarp();
+  if (renormalize)
+    for (int k = lane; k < top; k += 32) weight_of[static_cast<long long>(row) * top + k] /= chosen_sum;
+}
+
 // plan: [0 .. experts] first position of an expert's rows; [experts+1 .. 2 experts+1] first tile of an expert.
 __global__ void moe_plan_kernel(const int* __restrict__ counts, int experts, int* __restrict__ plan) {
   wait_for_prior_kernels();
@@ -108,7 +210,7 @@ template <typename TA, typename TC, bool kGated>
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ row_of, const TA* __restrict__ W0,
                    const TA* __restrict__ W1, long long expert_stride, TC* __restrict__ C, long long ldc,
-                   const int* __restrict__ plan, int experts, int N, int K) {
+                   const int* __restrict__ plan, int experts, int with_matrices, int N, int K) {
   constexpr int BM = kMoeTile, BN = 64, BK = 16, TM = 4, TN = 4;
   wait_for_prior_kernels();
   launch_dependents();
@@ -137,7 +239,7 @@ moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restric
   }
   __syncthreads();
   const int e = info[0];
-  if (e < 0) return;
+  if (e < 0 || e >= with_matrices) return;                      // (an identity expert has no matrices: its rows are the combine's)
   const int p0 = info[1], m_rows = info[2];
   if (tid < BM) rows_s[tid] = tid < m_rows ? (row_of != nullptr ? row_of[p0 + tid] : p0 + tid) : -1;
   __syncthreads();
@@ -224,13 +326,14 @@ template <typename T, typename TC, bool kGated>
 __global__ void __launch_bounds__(256)
 moe_gemv_kernel(const T* __restrict__ x, long long ldx, int row_div, const int* __restrict__ expert_of,
                 const T* __restrict__ W0, const T* __restrict__ W1, long long expert_stride, TC* __restrict__ out,
-                long long ldo, const int* __restrict__ out_index, int N, int K) {
+                long long ldo, const int* __restrict__ out_index, int with_matrices, int N, int K) {
   constexpr int kVec = 16 / sizeof(T), kCols = 4;
   extern __shared__ float xs[];
   wait_for_prior_kernels();
   launch_dependents();
   const int slot = blockIdx.x;
   const int e = expert_of[slot];
+  if (e >= with_matrices) return;                               // an identity expert: the combine takes the row itself
   const T* xr = x + static_cast<long long>(slot / row_div) * ldx;
   for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float<T>(xr[k]);
   __syncthreads();
@@ -318,9 +421,12 @@ batched_gemv_kernel(const T* __restrict__ x, long long ldx, long long batch_x, c
   }
 }
 
+// An expert from ``with_matrices`` on is an identity expert: its output is the row of x itself.
 template <typename T, typename TY>
 __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ pos_of,
-                                   const float* __restrict__ weight_of, T* __restrict__ out, int rows, int hidden, int top) {
+                                   const float* __restrict__ weight_of, T* __restrict__ out, int rows, int hidden, int top,
+                                   const int* __restrict__ expert_of, int with_matrices, const T* __restrict__ x,
+                                   long long ldx) {
   wait_for_prior_kernels();
   launch_dependents();
   const int row = blockIdx.x;
@@ -328,7 +434,9 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
     float acc = 0.0f;
     for (int k = 0; k < top; ++k) {
       const long long i = static_cast<long long>(row) * top + k;
-      acc = fmaf(weight_of[i], to_float<TY>(y[static_cast<long long>(pos_of[i]) * hidden + c]), acc);
+      const float v = expert_of[i] >= with_matrices ? to_float<T>(x[row * ldx + c])
+                                                    : to_float<TY>(y[static_cast<long long>(pos_of[i]) * hidden + c]);
+      acc = fmaf(weight_of[i], v, acc);
     }
     out[static_cast<long long>(row) * hidden + c] = from_float<T>(acc);
   }
@@ -371,14 +479,49 @@ extern "C" int pih_moe_route(const void* logits, int rows, int experts, int top,
   return 0;
 }
 
+// The same outputs as pih_moe_route from the scored routing (see moe_route_scored_kernel); logits fp32 [rows, ld] of which
+// the first ``experts`` columns are the router's outputs; correction fp32 [experts] or null.
+extern "C" int pih_moe_route_scored(const void* logits, long long ld, const void* correction, int rows, int experts, int top,
+                                    int groups, int keep, int renormalize, void* ints, void* weight_of, int grouped,
+                                    void* stream) {
+  if (rows <= 0) return 0;
+  if (experts < 1 || experts > 1024 || top < 1 || top > experts || groups < 1 || groups > 1024 || experts % groups ||
+      keep < 1 || keep > groups)
+    return PIH_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long slots = static_cast<long long>(rows) * top;
+  int* expert_of = static_cast<int*>(ints);
+  int* rank_of = expert_of + slots;
+  int* pos_of = rank_of + slots;
+  int* row_of = pos_of + slots;
+  int* counts = row_of + slots;
+  int* plan = counts + experts;
+  launch_kernel(moe_route_scored_kernel, dim3((rows + 3) / 4), dim3(128), 4 * 2 * groups * sizeof(float), s,
+                static_cast<const float*>(logits), ld, static_cast<const float*>(correction), rows, experts, top, groups,
+                keep, renormalize, expert_of, static_cast<float*>(weight_of), rank_of,
+                grouped ? counts : static_cast<int*>(nullptr), pos_of);
+  PIH_LAUNCH_CHECK();
+  if (!grouped) return 0;
+  launch_kernel(moe_plan_kernel, dim3(1), dim3(32), 0, s, static_cast<const int*>(counts), experts, plan);
+  PIH_LAUNCH_CHECK();
+  launch_kernel(moe_scatter_kernel, dim3(static_cast<unsigned>((slots + 255) / 256)), dim3(256), 0, s,
+                static_cast<const int*>(expert_of), static_cast<const int*>(rank_of), static_cast<const int*>(plan),
+                static_cast<int>(slots), top, pos_of, row_of);
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
 // x [rows, lda]; w_gate_up [experts, 2 ff, hidden]: an expert's gate rows, then its up rows; w_down [experts, hidden, ff];
 // act [slots, ff] (storage type); y fp32 [slots, hidden]; out [rows, hidden] (storage type).  few_rows: every slot on
 // its own (the weight rows streamed with 16-byte loads) instead of the grouped product; needs hidden and ff to be
-// multiples of 8 (bf16) or 4 (32-bit) and hidden, ff <= 12288.
+// multiples of 8 (bf16) or 4 (32-bit) and hidden, ff <= 12288.  ``experts`` counts the router's outputs, of which the
+// last ``identity`` have no matrices: their output is the row of x itself.
 extern "C" int pih_moe_experts(int dtype, const void* x, long long lda, const void* w_gate_up, const void* w_down, void* act,
                                void* y, void* out, const void* ints, const void* weight_of, int rows, int experts, int top,
-                               int hidden, int ff, int few_rows, void* stream) {
+                               int hidden, int ff, int few_rows, int identity, void* stream) {
   if (rows <= 0) return 0;
+  if (identity < 0 || identity > experts) return PIH_ERR_BAD_ARGUMENT;
+  const int with_matrices = experts - identity;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const long long slots = static_cast<long long>(rows) * top;
   const int* expert_of = static_cast<const int*>(ints);
@@ -399,26 +542,26 @@ extern "C" int pih_moe_experts(int dtype, const void* x, long long lda, const vo
       launch_kernel(moe_gemv_kernel<T, T, true>, dim3(static_cast<unsigned>(slots), (ff + 31) / 32), dim3(256),        \
                     hidden * sizeof(float), s, static_cast<const T*>(x), lda, top, expert_of, wgu,                     \
                     wgu + static_cast<long long>(ff) * hidden, gu_stride, static_cast<T*>(act),                        \
-                    static_cast<long long>(ff), static_cast<const int*>(nullptr), ff, hidden);                         \
+                    static_cast<long long>(ff), static_cast<const int*>(nullptr), with_matrices, ff, hidden);          \
       PIH_LAUNCH_CHECK();                                                                                              \
       launch_kernel(moe_gemv_kernel<T, float, false>, dim3(static_cast<unsigned>(slots), (hidden + 31) / 32),          \
                     dim3(256), ff * sizeof(float), s, static_cast<const T*>(act), static_cast<long long>(ff), 1,       \
                     expert_of, static_cast<const T*>(w_down), static_cast<const T*>(nullptr), down_stride,             \
-                    static_cast<float*>(y), static_cast<long long>(hidden), pos_of, hidden, ff);                       \
+                    static_cast<float*>(y), static_cast<long long>(hidden), pos_of, with_matrices, hidden, ff);        \
     } else {                                                                                                           \
       launch_kernel(moe_grouped_kernel<T, T, true>, dim3((ff + 63) / 64, tiles), dim3(256), 0, s,                      \
                     static_cast<const T*>(x), lda, row_of, wgu, wgu + static_cast<long long>(ff) * hidden, gu_stride,  \
-                    static_cast<T*>(act), static_cast<long long>(ff), plan, experts, ff, hidden);                      \
+                    static_cast<T*>(act), static_cast<long long>(ff), plan, experts, with_matrices, ff, hidden);       \
       PIH_LAUNCH_CHECK();                                                                                              \
       launch_kernel(moe_grouped_kernel<T, float, false>, dim3((hidden + 63) / 64, tiles), dim3(256), 0, s,             \
                     static_cast<const T*>(act), static_cast<long long>(ff), static_cast<const int*>(nullptr),          \
                     static_cast<const T*>(w_down), static_cast<const T*>(nullptr), down_stride,                        \
-                    static_cast<float*>(y), static_cast<long long>(hidden), plan, experts, hidden, ff);                \
+                    static_cast<float*>(y), static_cast<long long>(hidden), plan, experts, with_matrices, hidden, ff); \
     }                                                                                                                  \
     PIH_LAUNCH_CHECK();                                                                                                \
     launch_kernel(moe_combine_kernel<T, float>, dim3(rows), dim3(hidden >= 256 ? 256 : 128), 0, s,                     \
                   static_cast<const float*>(y), pos_of, static_cast<const float*>(weight_of), static_cast<T*>(out),    \
-                  rows, hidden, top);                                                                                  \
+                  rows, hidden, top, expert_of, with_matrices, static_cast<const T*>(x), lda);                         \
   } while (0)
   if (dtype == PIH_F32) PIH_MOE(float);
   else if (dtype == PIH_BF16) PIH_MOE(bf16);
@@ -429,14 +572,16 @@ extern "C" int pih_moe_experts(int dtype, const void* x, long long lda, const vo
 }
 
 // out[row] = sum_k weight_of[row][k] * y[pos_of[row][k]] for y in bf16 (the output of a library's grouped product)
+// (x [rows, ldx] and with_matrices: see moe_combine_kernel)
 extern "C" int pih_moe_combine_bf16(const void* y, const void* ints, const void* weight_of, void* out, int rows, int top,
-                                    int hidden, void* stream) {
+                                    int hidden, int with_matrices, const void* x, long long ldx, void* stream) {
   if (rows <= 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int* pos_of = static_cast<const int*>(ints) + 2LL * rows * top;
+  const int* expert_of = static_cast<const int*>(ints);
+  const int* pos_of = expert_of + 2LL * rows * top;
   launch_kernel(moe_combine_kernel<bf16, bf16>, dim3(rows), dim3(hidden >= 256 ? 256 : 128), 0, s,
                 static_cast<const bf16*>(y), pos_of, static_cast<const float*>(weight_of), static_cast<bf16*>(out), rows,
-                hidden, top);
+                hidden, top, expert_of, with_matrices, static_cast<const bf16*>(x), ldx);
   PIH_LAUNCH_CHECK();
   return 0;
 }

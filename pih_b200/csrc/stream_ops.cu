@@ -1,0 +1,144 @@
+// Row-wise kernels around a 32-bit residual stream whose norms sit on the sub-layers' outputs.
+//
+//   stream_cast       the stream rounded to the compute dtype (what a sub-layer reads)
+//   stream_norm_add   h += rmsnorm(y + bias) * w in 32-bit, and beside it the new h rounded to the compute dtype
+//   bias_xielu        act(z + b): for u > 0  ap u^2 + u / 2,  else  an (exp(u) - 1 - u) + u / 2   (32-bit inside)
+//   add_gated         out = a + sigmoid(g[row]) * b   (a shared expert behind its one-number gate)
+#include "common.cuh"
+
+namespace pih {
+
+template <typename TO>
+__global__ void stream_cast_kernel(const float* __restrict__ h, TO* __restrict__ out, long long n) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = from_float<TO>(h[i]);
+}
+
+// One block a row.  The sum of squares is taken over y + bias as it is (32-bit); the order of additions depends on the
+// block's size alone.
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256)
+stream_norm_add_kernel(float* __restrict__ h, const TY* __restrict__ y, long long ldy, const float* __restrict__ bias,
+                       const float* __restrict__ weight, TO* __restrict__ copy, int width, float eps) {
+  __shared__ float scratch[33];
+  wait_for_prior_kernels();
+  launch_dependents();
+  const long long row = blockIdx.x;
+  const TY* yr = y + row * ldy;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to_float<TY>(yr[c]) + (bias != nullptr ? bias[c] : 0.0f);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+  float* hr = h + row * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to_float<TY>(yr[c]) + (bias != nullptr ? bias[c] : 0.0f);
+    const float s = hr[c] + v * inv * weight[c];
+    hr[c] = s;
+    if (copy != nullptr) copy[row * width + c] = from_float<TO>(s);
+  }
+}
+
+template <typename T>
+__global__ void bias_xielu_kernel(const T* __restrict__ z, long long ldz, const float* __restrict__ bias, T* __restrict__ out,
+                                  long long rows, int width, float alpha_positive, float alpha_negative) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= rows * width) return;
+  const long long row = i / width;
+  const int c = static_cast<int>(i - row * width);
+  const float u = to_float<T>(z[row * ldz + c]) + (bias != nullptr ? bias[c] : 0.0f);
+  const float v = u > 0.0f ? fmaf(alpha_positive * u, u, 0.5f * u) : fmaf(alpha_negative, expm1f(u) - u, 0.5f * u);
+  out[i] = from_float<T>(v);
+}
+
+template <typename T>
+__global__ void add_gated_kernel(const T* __restrict__ a, const T* __restrict__ b, const float* __restrict__ gate,
+                                 long long ldg, T* __restrict__ out, long long rows, int width) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= rows * width) return;
+  const long long row = i / width;
+  const float g = 1.0f / (1.0f + expf(-gate[row * ldg]));
+  out[i] = from_float<T>(fmaf(g, to_float<T>(b[i]), to_float<T>(a[i])));
+}
+
+}  // namespace pih
+
+using namespace pih;
+typedef __nv_bfloat16 bf16;
+
+extern "C" int pih_stream_cast(int out_dtype, const void* h, void* out, long long n, void* stream) {
+  if (n <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(static_cast<unsigned>((n + 255) / 256));
+  if (out_dtype == PIH_BF16)
+    launch_kernel(stream_cast_kernel<bf16>, grid, dim3(256), 0, s, static_cast<const float*>(h), static_cast<bf16*>(out), n);
+  else if (out_dtype == PIH_F32)
+    launch_kernel(stream_cast_kernel<float>, grid, dim3(256), 0, s, static_cast<const float*>(h), static_cast<float*>(out), n);
+  else
+    return PIH_ERR_BAD_ARGUMENT;
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+// h fp32 [rows, width] (in place); y [rows, ldy] of y_dtype; bias, weight fp32 [width] (bias may be null); copy
+// [rows, width] of copy_dtype or null.
+extern "C" int pih_stream_norm_add(int y_dtype, int copy_dtype, void* h, const void* y, long long ldy, const void* bias,
+                                   const void* weight, void* copy, int rows, int width, float eps, void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(rows), block(width >= 1024 ? 256 : 128);
+#define PIH_SNA(TY, TO)                                                                                                \
+  launch_kernel(stream_norm_add_kernel<TY, TO>, grid, block, 0, s, static_cast<float*>(h), static_cast<const TY*>(y), \
+                ldy, static_cast<const float*>(bias), static_cast<const float*>(weight), static_cast<TO*>(copy), width, eps)
+  if (y_dtype == PIH_BF16 && copy_dtype == PIH_BF16) PIH_SNA(bf16, bf16);
+  else if (y_dtype == PIH_F32 && copy_dtype == PIH_F32) PIH_SNA(float, float);
+  else if (y_dtype == PIH_BF16 && copy_dtype == PIH_F32) PIH_SNA(bf16, float);
+  else if (y_dtype == PIH_F32 && copy_dtype == PIH_BF16) PIH_SNA(float, bf16);
+  else return PIH_ERR_BAD_ARGUMENT;
+#undef PIH_SNA
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+extern "C" int pih_bias_xielu(int dtype, const void* z, long long ldz, const void* bias, void* out, long long rows, int width,
+                              float alpha_positive, float alpha_negative, void* stream) {
+  if (rows <= 0 || width <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(static_cast<unsigned>((rows * width + 255) / 256));
+  if (dtype == PIH_BF16)
+    launch_kernel(bias_xielu_kernel<bf16>, grid, dim3(256), 0, s, static_cast<const bf16*>(z), ldz,
+                  static_cast<const float*>(bias), static_cast<bf16*>(out), rows, width, alpha_positive, alpha_negative);
+  else if (dtype == PIH_F32)
+    launch_kernel(bias_xielu_kernel<float>, grid, dim3(256), 0, s, static_cast<const float*>(z), ldz,
+                  static_cast<const float*>(bias), static_cast<float*>(out), rows, width, alpha_positive, alpha_negative);
+  else
+    return PIH_ERR_BAD_ARGUMENT;
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+// out = a + sigmoid(gate[row * ldg]) * b; a, b, out [rows, width] contiguous; gate fp32
+extern "C" int pih_add_gated(int dtype, const void* a, const void* b, const void* gate, long long ldg, void* out,
+                             long long rows, int width, void* stream) {
+  if (rows <= 0 || width <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(static_cast<unsigned>((rows * width + 255) / 256));
+  if (dtype == PIH_BF16)
+    launch_kernel(add_gated_kernel<bf16>, grid, dim3(256), 0, s, static_cast<const bf16*>(a), static_cast<const bf16*>(b),
+                  static_cast<const float*>(gate), ldg, static_cast<bf16*>(out), rows, width);
+  else if (dtype == PIH_F32)
+    launch_kernel(add_gated_kernel<float>, grid, dim3(256), 0, s, static_cast<const float*>(a), static_cast<const float*>(b),
+                  static_cast<const float*>(gate), ldg, static_cast<float*>(out), rows, width);
+  else
+    return PIH_ERR_BAD_ARGUMENT;
+  PIH_LAUNCH_CHECK();
+  return 0;
+}

@@ -69,6 +69,9 @@ class StepBatch:
     real_rows: int = 0                 # without padding
     real_requests: int = 0
     real_logit_rows: int = 0
+    # (stream, its rounding to the compute dtype): left by a block that keeps a 32-bit stream beside a 16-bit compute
+    # dtype, for the next block of the same forward pass
+    stream_copy: Optional[tuple] = None
 
 
 def _align(n: int, a: int = 4) -> int:

@@ -107,7 +107,9 @@ class CudaOps:
                      "pih_qk_attention_fused", "pih_gemm_tcgen05_pair", "pih_set_attention_side_by_side", "pih_set_skinny_rule",
                      "pih_gemm_simt_batched", "pih_embedding_stream", "pih_rmsnorm_stream", "pih_causal_conv",
                      "pih_gated_delta_rule", "pih_gated_rmsnorm", "pih_rglru_scan", "pih_latent_write",
-                     "pih_latent_attention_generic", "pih_moe_route", "pih_moe_experts", "pih_moe_combine_bf16", "pih_latent_attention_split", "pih_latent_attention_splits", "pih_latent_attention_mma", "pih_batched_gemv"):
+                     "pih_latent_attention_generic", "pih_moe_route", "pih_moe_experts", "pih_moe_combine_bf16", "pih_latent_attention_split", "pih_latent_attention_splits", "pih_latent_attention_mma", "pih_batched_gemv",
+                     "pih_stream_cast", "pih_stream_norm_add", "pih_bias_xielu", "pih_add_gated", "pih_retention",
+                     "pih_diff_qk_prepare", "pih_diff_attention_generic", "pih_moe_route_scored"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
         lib.pih_top_logprobs_scratch_words.restype = c_ll
@@ -777,7 +779,7 @@ class CudaOps:
     moe_library_min_slots = 65    # ... and from this many on the experts' products are the library's grouped product
 
     def moe_experts(self, x: torch.Tensor, logits: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
-                    top: int) -> torch.Tensor:
+                    top: int, routing: Optional[dict] = None) -> torch.Tensor:
         """Routed experts: per row the ``top`` largest of ``logits`` (fp32 ``[T, experts]``) choose, the softmax over
         the chosen weighs; ``out = sum_k weight_k * W_down_e (silu(W_gate_e x) * (W_up_e x))``.  ``w_gate_up``
         ``[experts, 2 ff, hidden]`` holds an expert's gate rows and then its up rows, ``w_down`` ``[experts, hidden, ff]``.
@@ -786,10 +788,18 @@ class CudaOps:
         the pack's grouped FMA product (an order of additions fixed by the row); in bf16 a step of few rows streams
         each chosen expert's rows once (a warp a column), and a step of many rows runs the library's grouped product
         (``torch._grouped_mm``: tensor cores, the groups' boundaries read on the device) where the pack's dense
-        products of many rows are the library's too."""
+        products of many rows are the library's too.
+
+        ``routing`` selects the other router: scores are the softmax over all ``outputs`` (the first columns of
+        ``logits``, whose rows may be longer), the choice goes by score plus ``correction`` within the
+        ``groups_keep`` best of ``groups`` groups, the chosen weigh with their scores (``renormalize``: divided by
+        their sum), and the outputs behind the experts that have matrices are identity experts (the row itself)."""
         T, hidden = x.shape
-        experts, ff = w_gate_up.shape[0], w_gate_up.shape[1] // 2
-        assert logits.dtype == torch.float32 and logits.is_contiguous() and logits.shape == (T, experts)
+        with_matrices, ff = w_gate_up.shape[0], w_gate_up.shape[1] // 2
+        experts = routing["outputs"] if routing is not None else with_matrices
+        identity = experts - with_matrices
+        assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[0] == T and identity >= 0
+        assert logits.shape[1] >= experts if routing is not None else (logits.is_contiguous() and logits.shape[1] == experts)
         assert x.stride(1) == 1 and w_gate_up.is_contiguous() and w_down.is_contiguous()
         slots = T * top
         bf16 = x.dtype == torch.bfloat16
@@ -799,27 +809,133 @@ class CudaOps:
         # (few rows: every slot is taken on its own, nothing is grouped or counted)
         ints = (torch.empty if few else torch.zeros)(int(words), dtype=torch.int32, device=x.device)
         weight_of = torch.empty(slots, dtype=torch.float32, device=x.device)
-        rc = self.lib.pih_moe_route(_ptr(logits), T, experts, top, _ptr(ints), _ptr(weight_of), 0 if few else 1, self._stream())
+        if routing is None:
+            rc = self.lib.pih_moe_route(_ptr(logits), T, experts, top, _ptr(ints), _ptr(weight_of), 0 if few else 1,
+                                        self._stream())
+        else:
+            rc = self.lib.pih_moe_route_scored(_ptr(logits), c_ll(logits.stride(0)), _ptr(routing.get("correction")), T,
+                                               experts, top, int(routing.get("groups", 1)), int(routing.get("groups_keep", 1)),
+                                               1 if routing.get("renormalize") else 0, _ptr(ints), _ptr(weight_of),
+                                               0 if few else 1, self._stream())
         self._check(rc, "moe_route")
         self.launches += 0 if few else 2
         out = torch.empty(T, hidden, dtype=x.dtype, device=x.device)
         if (bf16 and not few and slots >= self.moe_library_min_slots and hidden % 8 == 0 and ff % 8 == 0
                 and hasattr(torch, "_grouped_mm")):
             row_of = ints[3 * slots:4 * slots]
-            ends = ints[4 * slots + experts + 1:4 * slots + 2 * experts + 1]          # where each expert's rows end
+            ends = ints[4 * slots + experts + 1:4 * slots + experts + 1 + with_matrices]   # where each expert's rows end
+            # (the rows of identity experts lie behind the last of these: the grouped products leave them alone)
             xs = self.gather_rows(x, row_of) if x.is_contiguous() else x.index_select(0, row_of)
             gate_up = torch._grouped_mm(xs, w_gate_up.transpose(1, 2), offs=ends)     # [slots, 2 ff]
             act = self.silu_mul(gate_up)
             y = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends)             # [slots, hidden]
             rc = self.lib.pih_moe_combine_bf16(_ptr(y), _ptr(ints), _ptr(weight_of), _ptr(out), T, top, hidden,
-                                               self._stream())
+                                               with_matrices, _ptr(x), c_ll(x.stride(0)), self._stream())
             self._check(rc, "moe_combine")
             return out
         act = torch.empty(slots, ff, dtype=x.dtype, device=x.device)
         y = torch.empty(slots, hidden, dtype=torch.float32, device=x.device)
         rc = self.lib.pih_moe_experts(_DT[x.dtype], _ptr(x), c_ll(x.stride(0)), _ptr(w_gate_up), _ptr(w_down), _ptr(act),
                                       _ptr(y), _ptr(out), _ptr(ints), _ptr(weight_of), T, experts, top, hidden, ff,
-                                      1 if few else 0, self._stream())
+                                      1 if few else 0, identity, self._stream())
         self._check(rc, "moe_experts")
         self.launches += 2
+        return out
+
+    # -- norms on the sub-layers' outputs, retention, differential attention, a biased feed-forward ---------------------
+    def stream_cast(self, h: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        """A 32-bit stream rounded to ``dtype``."""
+        assert h.dtype == torch.float32 and h.is_contiguous()
+        out = torch.empty(h.shape, dtype=dtype, device=h.device)
+        rc = self.lib.pih_stream_cast(_DT[dtype], _ptr(h), _ptr(out), c_ll(h.numel()), self._stream())
+        self._check(rc, "stream_cast")
+        return out
+
+    def stream_norm_add(self, h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
+                        bias: Optional[torch.Tensor] = None, copy_dtype: Optional[torch.dtype] = None):
+        """``h += rmsnorm(y + bias) * weight`` in place on the stream ``h`` (32-bit sums; ``h`` may be a 32-bit path's
+        stream or a 32-bit stream beside a 16-bit compute dtype); with ``copy_dtype`` returns the new ``h`` rounded to
+        it (what the next sub-layer reads), else None."""
+        rows, width = h.shape
+        assert h.dtype == torch.float32 and h.is_contiguous() and y.shape == h.shape and y.stride(1) == 1
+        weight = weight if weight.dtype == torch.float32 else weight.float()
+        copy = torch.empty(rows, width, dtype=copy_dtype, device=h.device) if copy_dtype is not None else None
+        rc = self.lib.pih_stream_norm_add(_DT[y.dtype], _DT[copy_dtype] if copy_dtype is not None else _DT[y.dtype], _ptr(h),
+                                          _ptr(y), c_ll(y.stride(0)), _ptr(bias), _ptr(weight), _ptr(copy), rows, width,
+                                          c_float(eps), self._stream())
+        self._check(rc, "stream_norm_add")
+        return copy
+
+    def bias_xielu(self, z: torch.Tensor, bias: Optional[torch.Tensor], alpha_positive: float,
+                   alpha_negative: float) -> torch.Tensor:
+        """xIELU of ``z + bias``: ``alpha_positive u^2 + u / 2`` for u > 0, else ``alpha_negative (exp(u) - 1 - u) + u / 2``
+        (32-bit inside, rounded once)."""
+        rows, width = z.shape
+        assert z.stride(1) == 1 and (bias is None or bias.dtype == torch.float32)
+        out = torch.empty(rows, width, dtype=z.dtype, device=z.device)
+        rc = self.lib.pih_bias_xielu(_DT[z.dtype], _ptr(z), c_ll(z.stride(0)), _ptr(bias), _ptr(out), c_ll(rows), width,
+                                     c_float(alpha_positive), c_float(alpha_negative), self._stream())
+        self._check(rc, "bias_xielu")
+        return out
+
+    def add_gated(self, a: torch.Tensor, b: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+        """``a + sigmoid(gate[row]) * b``: a, b ``[T, width]``; gate fp32 ``[T]`` (a view of logits)."""
+        rows, width = a.shape
+        assert a.is_contiguous() and b.is_contiguous() and b.shape == a.shape and gate.dtype == torch.float32
+        out = torch.empty_like(a)
+        rc = self.lib.pih_add_gated(_DT[a.dtype], _ptr(a), _ptr(b), _ptr(gate), c_ll(gate.stride(0)), _ptr(out), c_ll(rows),
+                                    width, self._stream())
+        self._check(rc, "add_gated")
+        return out
+
+    def retention(self, qk: torch.Tensor, v: torch.Tensor, *, frequencies: Optional[torch.Tensor],
+                  decay_minus_one: torch.Tensor, key_scale: float, state: torch.Tensor, step, heads: int, key_dim: int,
+                  value_dim: int) -> torch.Tensor:
+        """Retention over the step's rows, request by request from each one's state slot (``state[slot]`` is
+        ``S [heads, key_dim, value_dim]``): q and k (``qk [T, 2 heads key_dim]``, a view) are rotated by the row's
+        position with ``frequencies`` (fp32 ``[rotary_dim / 2]``; None: no rotation), k then times ``key_scale``;
+        ``S <- S + decay_minus_one S + k v^T``; returns the read-outs ``S^T q``, fp32 ``[T, heads, value_dim]``."""
+        T = qk.shape[0]
+        assert qk.stride(1) == 1 and v.stride(1) == 1 and v.dtype == qk.dtype and state.dtype == torch.float32
+        scratch = torch.empty(2 * T * heads * key_dim, dtype=torch.float32, device=qk.device)
+        out = torch.empty(T, heads, value_dim, dtype=torch.float32, device=qk.device)
+        rot = 2 * frequencies.shape[0] if frequencies is not None else 0
+        rc = self.lib.pih_retention(_DT[qk.dtype], _ptr(qk), c_ll(qk.stride(0)), _ptr(v), c_ll(v.stride(0)), _ptr(frequencies),
+                                    rot, _ptr(step.positions), _ptr(decay_minus_one), c_float(key_scale), _ptr(scratch),
+                                    _ptr(out), _ptr(state), c_ll(state.stride(0)), _ptr(step.cu_q), _ptr(step.state_slots),
+                                    T, step.num_requests, heads, key_dim, value_dim, self._stream())
+        self._check(rc, "retention")
+        self.launches += 1                                     # two kernels
+        return out
+
+    def diff_qk_prepare(self, qkv: torch.Tensor, *, q_norm, k_norm, eps: float, frequencies, positions, slot_mapping,
+                        cache: torch.Tensor, write_kv: bool, heads: int, kv_heads: int, key_dim: int, value_dim: int) -> None:
+        """Per-map RMS norm (fp32 weights ``[key_dim]`` or None) and rotation of the q and k maps of the rows
+        ``[q: heads x 2 x key_dim | k: kv_heads x 2 x key_dim | v: kv_heads x value_dim]``: q is changed in place, and
+        with ``write_kv`` k and v go to the rows' slots of ``cache [pages, page_size, kv_heads (2 key_dim + value_dim)]``
+        (without it the rows hold q alone)."""
+        rows = qkv.shape[0]
+        num_pages, page_size, width = cache.shape
+        assert qkv.stride(1) == 1 and cache.dtype == qkv.dtype and width == kv_heads * (2 * key_dim + value_dim)
+        rot = 2 * frequencies.shape[0] if frequencies is not None else 0
+        rc = self.lib.pih_diff_qk_prepare(_DT[qkv.dtype], _ptr(qkv), c_ll(qkv.stride(0)), _ptr(q_norm), _ptr(k_norm),
+                                          c_float(eps), _ptr(frequencies), rot, _ptr(positions), _ptr(slot_mapping),
+                                          _ptr(cache), page_size, num_pages, rows, heads, kv_heads, key_dim, value_dim,
+                                          1 if write_kv else 0, self._err(), self._stream())
+        self._check(rc, "diff_qk_prepare")
+
+    def diff_attention(self, qkv: torch.Tensor, *, cache: torch.Tensor, block_table: torch.Tensor, step, scale: float,
+                       lam: float, out_scale: float, norm_eps: float, window: int, heads: int, kv_heads: int, key_dim: int,
+                       value_dim: int) -> torch.Tensor:
+        """Differential attention of the step's rows (their q maps, prepared, in the first columns of ``qkv``) over the
+        cache: per head ``softmax_1 v - lam * softmax_2 v``, divided by its root mean square (``norm_eps``) and times
+        ``out_scale``.  Returns ``[T, heads * value_dim]`` in the compute dtype."""
+        rows = qkv.shape[0]
+        num_pages, page_size = cache.shape[0], cache.shape[1]
+        out = torch.empty(rows, heads * value_dim, dtype=qkv.dtype, device=qkv.device)
+        rc = self.lib.pih_diff_attention_generic(
+            _DT[qkv.dtype], _ptr(qkv), c_ll(qkv.stride(0)), _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1],
+            _ptr(step.request_of_row), _ptr(step.positions), rows, heads, kv_heads, key_dim, value_dim, page_size, num_pages,
+            c_float(scale), c_float(lam), c_float(out_scale), c_float(norm_eps), int(window), self._err(), self._stream())
+        self._check(rc, "diff_attention_generic")
         return out

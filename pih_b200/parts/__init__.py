@@ -1,7 +1,8 @@
 """Model parts: mixers, feed-forwards, norms, position encodings, blocks."""
 from .registry import (PagedKVNeed, PagedVectorNeed, Runtime, StateNeed, TensorInfo, part_class, register_block,
                        register_ffn, register_mixer, register_norm, register_position, unregister)
-from . import norm, rope, attention, swiglu, block, gated_delta, rglru, latent_attention, moe  # noqa: F401  (registers the built-in kinds)
+from . import (norm, rope, attention, swiglu, block, gated_delta, rglru, latent_attention, moe, retention,  # noqa: F401
+               diff_attention, biased_mlp, scored_moe)                 # (registers the built-in kinds)
 
 __all__ = ["PagedKVNeed", "PagedVectorNeed", "Runtime", "StateNeed", "TensorInfo", "part_class", "register_block",
            "register_ffn", "register_mixer", "register_norm", "register_position", "unregister"]

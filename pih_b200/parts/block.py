@@ -74,3 +74,45 @@ class PreNormBlock:
         if fused_post and hasattr(self.ffn, "forward_prenorm"):
             return self.ffn.forward_prenorm(h, a, self.norm_post)
         return h, self.ffn.forward(self.norm_post.add_forward(h, a))
+
+
+@register_block("outnorm")
+class OutNormBlock:
+    """``h += norm_in(mixer(h)); h += norm_post(ffn(h))``: the norms sit on the sub-layers' outputs and the sub-layers
+    read the stream itself.  The stream ``h`` is 32-bit; a sub-layer reads its rounding to the compute dtype, which the
+    kernel that adds a normed output to the stream writes beside the sum (``step.stream_copy`` hands the last one to
+    the next block, so that only the first block of a step has to round the stream itself).  A bias that a
+    feed-forward adds to its output (``ffn.output_bias``) is added by the same kernel, before the norm."""
+
+    @classmethod
+    def expected_tensors(cls, spec):
+        return PreNormBlock.expected_tensors.__func__(cls, spec)
+
+    def __init__(self, spec, weights, rt: Runtime):
+        PreNormBlock.__init__(self, spec, weights, rt)
+        for norm in (self.norm_in, self.norm_post):
+            if norm is not None and not hasattr(norm, "weight"):
+                raise TypeError("a norm on a sub-layer's output needs a weight vector")
+
+    def _input(self, h, step):
+        if h.dtype == self.rt.dtype:
+            return h
+        held = getattr(step, "stream_copy", None)
+        if held is not None and held[0] is h:
+            return held[1]
+        return self.rt.ops.stream_cast(h, self.rt.dtype)
+
+    def _add(self, h, y, norm, step, bias=None):
+        ops = self.rt.ops
+        x = ops.stream_norm_add(h, y, norm.weight, norm.spec.eps, bias=bias,
+                                copy_dtype=self.rt.dtype if h.dtype != self.rt.dtype else None)
+        step.stream_copy = (h, x) if x is not None else None
+
+    def forward(self, h, delta, step, cache):
+        if delta is not None:
+            raise ValueError("a block with norms on its outputs takes a stream with nothing left to add")
+        self._add(h, self.mixer.forward(self._input(h, step), step, cache), self.norm_in, step)
+        if self.ffn is not None:
+            y = self.ffn.forward(self._input(h, step))
+            self._add(h, y, self.norm_post, step, bias=getattr(self.ffn, "output_bias", None))
+        return h, None

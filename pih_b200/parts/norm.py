@@ -23,12 +23,12 @@ class RMSNorm:
 
     @classmethod
     def expected_tensors(cls, spec):
-        return {"weight": TensorInfo((spec.width,), "one_plus_normal")}
+        return {getattr(spec, "weight_name", "weight"): TensorInfo((spec.width,), "one_plus_normal")}
 
     def __init__(self, spec, weights, rt: Runtime):
         self.spec = spec
         self.rt = rt
-        self.weight = bind_vector(weights["weight"], rt)
+        self.weight = bind_vector(weights[getattr(spec, "weight_name", "weight")], rt)
 
     def forward(self, x, rows=None):
         return self.add_forward(x, None, rows=rows)

@@ -43,3 +43,30 @@ class RotaryEncoding:
     def rotation_table(self):
         """fp32 [max_positions, rotary_dim/2, 2] holding (cos, sin)."""
         return self._table
+
+
+@register_position("rope_computed")
+class ComputedRotary:
+    """The same rotate-half rotation without a table: the mixer's kernel forms ``angle = position * f_i`` in 32-bit
+    from the frequencies ``f_i = theta^(-2i/rotary_dim)`` (computed in double here, rounded once) and takes its
+    cosine and sine there.  No longest context has to be known."""
+
+    @classmethod
+    def expected_tensors(cls, spec):
+        return {}
+
+    def __init__(self, spec, weights, rt: Runtime):
+        if spec.rotary_dim % 2 or not 0 < spec.rotary_dim <= spec.head_dim:
+            raise ValueError(f"rotary_dim must be even and within head_dim, got {spec.rotary_dim}")
+        self.spec = spec
+        self.rotary_dim = spec.rotary_dim
+        pair = torch.arange(spec.rotary_dim // 2, dtype=torch.float64)
+        inv = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * pair / spec.rotary_dim)
+        self._frequencies = inv.to(torch.float32).to(rt.device).contiguous()
+
+    def rotation_table(self):
+        return None
+
+    def frequencies(self):
+        """fp32 [rotary_dim / 2]."""
+        return self._frequencies
