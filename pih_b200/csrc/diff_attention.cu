@@ -108,7 +108,11 @@ diff_attention_generic_kernel(const T* __restrict__ qkv, long long ld, T* __rest
   if (unit >= static_cast<long long>(rows) * heads) return;
   const int row = static_cast<int>(unit / heads), head = static_cast<int>(unit % heads);
   const int req = request_of_row[row];
-  if (req < 0) return;
+  if (req < 0) {                                           // a row of padding: zeros, so that nothing unset travels on
+    T* o = out + static_cast<long long>(row) * heads * vdim + static_cast<long long>(head) * vdim;
+    for (int e = lane; e < vdim; e += 32) o[e] = from_float<T>(0.0f);
+    return;
+  }
   const int g = head / (heads / kv_heads);
   const long long width = static_cast<long long>(kv_heads) * (2 * dim + vdim);
   float* q = smem + warp * 2 * dim;                        // map 1 | map 2

@@ -278,9 +278,37 @@ class FakeOps:
             out[t] = o
         return out.to(q.dtype)
 
-    def moe_experts(self, x, logits, w_gate_up, w_down, top):
+    @staticmethod
+    def _scored_choice(logits, top, routing):
+        n = routing["outputs"]
+        s = torch.softmax(logits[:, :n].float(), dim=-1)
+        c = s + (routing["correction"] if routing.get("correction") is not None else 0.0)
+        groups, keep = routing.get("groups", 1), routing.get("groups_keep", 1)
+        if groups > 1:
+            best = c.view(-1, groups, n // groups).max(-1).values
+            order = torch.argsort(best, dim=-1, descending=True, stable=True)[:, :keep]
+            kept = torch.zeros_like(best, dtype=torch.bool).scatter_(1, order, True)
+            c = torch.where(kept.repeat_interleave(n // groups, dim=1), c, torch.full_like(c, float("-inf")))
+        idx = torch.argsort(c, dim=-1, descending=True, stable=True)[:, :top]
+        wt = torch.gather(s, 1, idx)
+        return idx, wt / wt.sum(-1, keepdim=True) if routing.get("renormalize") else wt
+
+    def moe_experts(self, x, logits, w_gate_up, w_down, top, routing=None):
         ff = w_gate_up.shape[1] // 2
         w_gate, w_up = w_gate_up[:, :ff], w_gate_up[:, ff:]
+        if routing is not None:
+            idx, wt = self._scored_choice(logits, top, routing)
+            out = torch.zeros(x.shape, dtype=torch.float32)
+            xf = x.float()
+            for t in range(x.shape[0]):
+                for j in range(top):
+                    e = int(idx[t, j])
+                    if e >= w_gate_up.shape[0]:                                  # an identity expert
+                        out[t] += wt[t, j] * xf[t]
+                        continue
+                    a = torch.nn.functional.silu(xf[t] @ w_gate[e].float().T) * (xf[t] @ w_up[e].float().T)
+                    out[t] += wt[t, j] * (a @ w_down[e].float().T)
+            return out.to(x.dtype)
         val, idx = torch.topk(logits, top, dim=-1)
         wt = torch.softmax(val, dim=-1)
         out = torch.zeros(x.shape, dtype=torch.float32)
@@ -292,3 +320,94 @@ class FakeOps:
                 a = ((g * torch.sigmoid(g)) * u).to(x.dtype).float()
                 out[t] += wt[t, j] * (a @ w_down[e].float().T)
         return out.to(x.dtype)
+
+    # -- norms on the sub-layers' outputs, retention, differential attention, a biased feed-forward ---------------------
+    def stream_cast(self, h, dtype):
+        return h.to(dtype)
+
+    def stream_norm_add(self, h, y, weight, eps, bias=None, copy_dtype=None):
+        v = y.float() + (bias if bias is not None else 0.0)
+        h += v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * weight.float()
+        return h.to(copy_dtype) if copy_dtype is not None else None
+
+    def bias_xielu(self, z, bias, alpha_positive, alpha_negative):
+        u = z.float() + (bias if bias is not None else 0.0)
+        v = torch.where(u > 0, alpha_positive * u * u + 0.5 * u, alpha_negative * (torch.expm1(u.clamp(max=0.0)) - u) + 0.5 * u)
+        return v.to(z.dtype)
+
+    def add_gated(self, a, b, gate):
+        return (a.float() + torch.sigmoid(gate)[:, None] * b.float()).to(a.dtype)
+
+    @staticmethod
+    def _rotate(x, positions, frequencies):
+        """x [T, n, d]: rotate-half over the first 2 * len(frequencies) columns."""
+        if frequencies is None:
+            return x
+        half = frequencies.shape[0]
+        ang = positions.float()[:, None] * frequencies[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        u, v = x[..., :half], x[..., half:2 * half]
+        return torch.cat([u * c - v * s, v * c + u * s, x[..., 2 * half:]], dim=-1)
+
+    def retention(self, qk, v, *, frequencies, decay_minus_one, key_scale, state, step, heads, key_dim, value_dim):
+        T = qk.shape[0]
+        QK = heads * key_dim
+        q = self._rotate(qk[:, :QK].float().view(T, heads, key_dim), step.positions, frequencies)
+        k = self._rotate(qk[:, QK:].float().view(T, heads, key_dim), step.positions, frequencies) * key_scale
+        vv = v.float().view(T, heads, value_dim)
+        out = torch.zeros(T, heads, value_dim)
+        for lo, hi, slot in self._requests(step):
+            S = state[slot].view(heads, key_dim, value_dim)
+            for t in range(lo, hi):
+                S += decay_minus_one[:, None, None] * S + k[t][:, :, None] * vv[t][:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", S, q[t])
+        return out
+
+    def diff_qk_prepare(self, qkv, *, q_norm, k_norm, eps, frequencies, positions, slot_mapping, cache, write_kv, heads,
+                        kv_heads, key_dim, value_dim):
+        T = qkv.shape[0]
+        nq, nk = heads * 2 * key_dim, kv_heads * 2 * key_dim
+
+        def prepared(x, w):
+            x = x.float().view(T, -1, key_dim)
+            if w is not None:
+                x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
+            return self._rotate(x, positions, frequencies).reshape(T, -1)
+
+        qkv[:, :nq] = prepared(qkv[:, :nq], q_norm).to(qkv.dtype)
+        if write_kv:
+            k = prepared(qkv[:, nq:nq + nk], k_norm)
+            flat = cache.view(-1, cache.shape[-1])
+            for t, slot in enumerate(slot_mapping.tolist()):
+                if slot == -2:
+                    continue
+                assert slot >= 0
+                flat[slot, :nk] = k[t].to(cache.dtype)
+                flat[slot, nk:] = qkv[t, nq + nk:]
+
+    def diff_attention(self, qkv, *, cache, block_table, step, scale, lam, out_scale, norm_eps, window, heads, kv_heads,
+                       key_dim, value_dim):
+        T = qkv.shape[0]
+        page_size = cache.shape[1]
+        nk = kv_heads * 2 * key_dim
+        out = torch.zeros(T, heads, value_dim)
+        for t in range(T):
+            r = int(step.request_of_row[t])
+            if r < 0:
+                continue
+            p = int(step.positions[t])
+            js = torch.arange(max(0, p - window + 1) if window else 0, p + 1)
+            pages = block_table[r, (js // page_size).long()].long()
+            if not (pages >= 0).all():
+                self._report(2)
+                pages = pages.clamp(min=0)
+            C = cache[pages, (js % page_size).long()].float()
+            K = C[:, :nk].view(-1, kv_heads, 2, key_dim)
+            V = C[:, nk:].view(-1, kv_heads, value_dim)
+            q = qkv[t, :heads * 2 * key_dim].float().view(heads, 2, key_dim)
+            for h in range(heads):
+                g = h // (heads // kv_heads)
+                a = [torch.softmax((K[:, g, j] @ q[h, j]) * scale, dim=0) @ V[:, g] for j in range(2)]
+                out[t, h] = a[0] - lam * a[1]
+        out = out / torch.sqrt((out * out).mean(-1, keepdim=True) + norm_eps) * out_scale
+        return out.reshape(T, heads * value_dim).to(qkv.dtype)
