@@ -307,6 +307,34 @@ def _rigotar_config(width: int, layers: int, kinds=("rglru", "latent_attention",
                        for i in range(layers)]}
 
 
+def _tuganex_config(width: int, layers: int, kinds=("attention", "retention"), mlps=("dense", "moe"), vocab: int = 32768,
+                    share_from: int = -1):
+    """Layer sizes that resemble a real model's at this width: heads of two 64-wide maps (128-wide retention keys) and
+    128-wide values, half as many key/value heads, a dense feed-forward of three times the width, and sixteen experts
+    with two identity experts in three groups of which two are kept, two chosen, and a shared expert.  ``share_from``:
+    from this layer on, attention layers read the keys and values of the first attention layer."""
+    heads = width // 128
+    rot = {"dims": 64, "base": 1e6}
+    mixers = {"attention": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 64, "vdim": 128, "rot": rot,
+                            "scale": 0.125, "diff": 0.5},
+              "retention": {"heads": heads, "dim": 128, "vdim": 128, "rot": rot,
+                            "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(1, heads - 1)) for h in range(heads)]}}
+    ffs = {"dense": {"kind": "dense", "ff": 3 * width}, None: None,
+           "moe": {"kind": "moe", "router": {"experts": 16, "identity": 2, "top": 2, "groups": {"count": 3, "keep": 2}},
+                   "expert": {"ff": 3 * width // 2}, "shared": {"ff": width // 2}}}
+    out, first_attention = [], None
+    for i in range(layers):
+        kind = kinds[i % len(kinds)]
+        mixer = dict(mixers[kind])
+        if kind == "attention":
+            if first_attention is None:
+                first_attention = i
+            elif 0 <= share_from <= i:
+                mixer["kv_from"] = first_attention
+        out.append({"type": kind, "mixer": mixer, "mlp": ffs[mlps[(i // len(kinds)) % len(mlps)] if mlps else None]})
+    return {"architecture": "Tuganex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
+
+
 def _dense_config(width: int, layers: int, vocab: int = 32768):
     return dict(QWEN3_0_6B, hidden_size=width, intermediate_size=3 * width, num_hidden_layers=layers,
                 num_attention_heads=width // 128 * 2, num_key_value_heads=width // 128, head_dim=128, vocab_size=vocab,
@@ -378,11 +406,24 @@ def design_run(args) -> int:
     batch, context, prompt, steps = args.batch, CONTEXT, PREFILL_TOKENS, max(8, args.steps // 4)
     with ClockSampler() as clocks:
         for width in (1024, 2048):
-            cases = [("rigotar", _rigotar_config(width, 8)), ("dense", _dense_config(width, 8))]
-            if width == 1024:
-                cases += [(f"rigotar {k} x4, no feed-forward", _rigotar_config(width, 4, kinds=(k,), moe=False))
-                          for k in ("rglru", "latent_attention", "delta")]
-                cases += [("rigotar rglru x4 with experts", _rigotar_config(width, 4, kinds=("rglru",)))]
+            if args.design == "tuganex":
+                # the design beside the two models that are nearest to it (mixers with a state and routed experts; a
+                # softmax attention and a dense feed-forward), and each of its kinds of layer alone beside its like
+                cases = [("tuganex", _tuganex_config(width, 8, share_from=6)), ("rigotar", _rigotar_config(width, 8)),
+                         ("dense", _dense_config(width, 8))]
+                if width == 1024:
+                    cases += [(f"tuganex {k} x4, no feed-forward", _tuganex_config(width, 4, kinds=(k,), mlps=None))
+                              for k in ("retention", "attention")]
+                    cases += [("rigotar delta x4, no feed-forward", _rigotar_config(width, 4, kinds=("delta",), moe=False)),
+                              ("tuganex retention x4, dense feed-forward", _tuganex_config(width, 4, kinds=("retention",), mlps=("dense",))),
+                              ("tuganex retention x4 with experts", _tuganex_config(width, 4, kinds=("retention",), mlps=("moe",))),
+                              ("rigotar delta x4 with experts", _rigotar_config(width, 4, kinds=("delta",)))]
+            else:
+                cases = [("rigotar", _rigotar_config(width, 8)), ("dense", _dense_config(width, 8))]
+                if width == 1024:
+                    cases += [(f"rigotar {k} x4, no feed-forward", _rigotar_config(width, 4, kinds=(k,), moe=False))
+                              for k in ("rglru", "latent_attention", "delta")]
+                    cases += [("rigotar rglru x4 with experts", _rigotar_config(width, 4, kinds=("rglru",)))]
             for name, raw in cases:
                 model = _build(raw)
                 pre_ms, dec_ms = _timed_steps(model, batch, context, prompt, steps)
@@ -393,7 +434,8 @@ def design_run(args) -> int:
                 gc.collect()
                 torch.cuda.empty_cache()
         clock_summary = clocks.summary()
-    print(json.dumps({"metric": "prompt and decode tok/s of the Rigotar design beside the dense decoder", "dtype": "bf16",
+    print(json.dumps({"metric": f"prompt and decode tok/s of the {args.design.capitalize()} design beside the framework's other models",
+                      "dtype": "bf16",
                       "data": "synthetic", "n_gpus": 1, "config": {"prompt_tokens": prompt, "decode_batch": batch,
                                                                    "context": context, "page_size": PAGE},
                       "rows": rows, "clocks": clock_summary}))
@@ -419,7 +461,7 @@ def main() -> int:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
-    ap.add_argument("--design", default=None, choices=["rigotar"],
+    ap.add_argument("--design", default=None, choices=["rigotar", "tuganex"],
                     help="instead of the recorded workload: this design's prompt and decode throughput beside the dense decoder's")
     ap.add_argument("--plain-launches", action="store_true",
                     help="launch kernels fully serialised instead of with programmatic dependent launch")
@@ -432,7 +474,7 @@ def main() -> int:
     if args.warmup < 3:
         args.warmup = 3
 
-    if args.design == "rigotar":
+    if args.design is not None:
         return design_run(args)
 
     import torch

@@ -8,7 +8,14 @@
 //   diff_attention_generic   a warp a (row, head): keys in chunks of 32 at fixed places (a lane a key for the scores,
 //                            a lane a value column for the sums), both maps side by side, 32-bit throughout; the
 //                            result does not depend on the step's make-up by a single bit
+//   diff_attention_tile      bf16, tensor cores (mma.sync m16n8k16), requests of more than 16 rows: a warp 16 rows of a
+//                            (request, head), a block 4 such warps that share tiles of 64 keys fetched by cp.async into
+//                            two buffers; scores, softmax and sums 32-bit; the weights enter the product with the
+//                            values as a bf16 pair (rounding and remainder), so that they count with 16 bits
+//   diff_attention_split     requests of at most 16 rows: the keys of a (row, head) cut into parts side by side (the
+//                            generic kernel's loop over a stretch of keys), then diff_attention_merge in order
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace pih {
 
@@ -93,42 +100,18 @@ __device__ __forceinline__ void diff_finish(const float* a1, const float* a2, fl
     if (lane + 32 * e < vdim) out[lane + 32 * e] = from_float<T>(o[e] * inv);
 }
 
+// The sums of both maps of one (row, head) over the keys first .. last (absolute places; chunks of 32 at multiples of
+// 32): a lane a key for the scores, a lane a value column (lane + 32 e) for the sums.  q: 32-bit, [map 1 | map 2].
 template <typename T>
-__global__ void __launch_bounds__(128)
-diff_attention_generic_kernel(const T* __restrict__ qkv, long long ld, T* __restrict__ out, const T* __restrict__ cache,
-                              const int* __restrict__ block_table, int table_width, const int* __restrict__ request_of_row,
-                              const int* __restrict__ positions, int rows, int heads, int kv_heads, int dim, int vdim,
-                              int page_size, int num_pages, float scale, float lam, float out_scale, float eps, int window,
-                              uint32_t* __restrict__ error) {
-  extern __shared__ float smem[];
-  wait_for_prior_kernels();
-  launch_dependents();
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const long long unit = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
-  if (unit >= static_cast<long long>(rows) * heads) return;
-  const int row = static_cast<int>(unit / heads), head = static_cast<int>(unit % heads);
-  const int req = request_of_row[row];
-  if (req < 0) {                                           // a row of padding: zeros, so that nothing unset travels on
-    T* o = out + static_cast<long long>(row) * heads * vdim + static_cast<long long>(head) * vdim;
-    for (int e = lane; e < vdim; e += 32) o[e] = from_float<T>(0.0f);
-    return;
-  }
-  const int g = head / (heads / kv_heads);
+__device__ __forceinline__ void diff_stretch(const float* q, const T* __restrict__ cache, const int* __restrict__ table,
+                                             int first, int last, int g, int kv_heads, int dim, int vdim, int page_size,
+                                             int num_pages, float scale, int lane, float (&a1)[kDiffMaxPerLane],
+                                             float (&a2)[kDiffMaxPerLane], float& m1, float& m2, float& l1, float& l2,
+                                             uint32_t* __restrict__ error) {
   const long long width = static_cast<long long>(kv_heads) * (2 * dim + vdim);
-  float* q = smem + warp * 2 * dim;                        // map 1 | map 2
-  const T* qr = qkv + row * ld + static_cast<long long>(head) * 2 * dim;
-  for (int e = lane; e < 2 * dim; e += 32) q[e] = to_float<T>(qr[e]);
-  __syncwarp();
-  const int pos = positions[row];
-  const int first = window > 0 ? max(0, pos - window + 1) : 0;
-  const int* table = block_table + static_cast<long long>(req) * table_width;
-  float a1[kDiffMaxPerLane], a2[kDiffMaxPerLane];
-#pragma unroll
-  for (int e = 0; e < kDiffMaxPerLane; ++e) a1[e] = a2[e] = 0.0f;
-  float m1 = -INFINITY, m2 = -INFINITY, l1 = 0.0f, l2 = 0.0f;
-  for (int j0 = first & ~31; j0 <= pos; j0 += 32) {
+  for (int j0 = first & ~31; j0 <= last; j0 += 32) {
     const int j = j0 + lane;
-    const bool live = j >= first && j <= pos;
+    const bool live = j >= first && j <= last;
     long long at = -1;
     if (live) {
       const int page = table[j / page_size];
@@ -147,7 +130,7 @@ diff_attention_generic_kernel(const T* __restrict__ qkv, long long ld, T* __rest
       s2 = d2 * scale;
     }
     const float n1 = fmaxf(m1, warp_max(s1)), n2 = fmaxf(m2, warp_max(s2));
-    if (n1 == -INFINITY) continue;                          // (no live key in the chunk: cannot happen for j0 <= pos)
+    if (n1 == -INFINITY) continue;                          // no live key in the chunk
     const float p1 = at >= 0 ? expf(s1 - n1) : 0.0f, p2 = at >= 0 ? expf(s2 - n2) : 0.0f;
     const float c1 = expf(m1 - n1), c2 = expf(m2 - n2);    // exp(-inf) = 0 at the first chunk
     l1 = fmaf(l1, c1, warp_sum(p1));
@@ -172,12 +155,350 @@ diff_attention_generic_kernel(const T* __restrict__ qkv, long long ld, T* __rest
       }
     }
   }
+}
+
+// A warp a (row, head) and a part of its keys.  splits == 1: the whole row, finished here (``partial`` unused).  More:
+// part ``blockIdx.y`` of the keys of rows whose request brings at most ``small_rows`` rows (the others are the tile
+// kernel's), its sums to ``partial`` [row][head][split][4 + 2 vdim]: m1, l1, m2, l2, a1, a2.
+template <typename T>
+__global__ void __launch_bounds__(128)
+diff_attention_generic_kernel(const T* __restrict__ qkv, long long ld, T* __restrict__ out, const T* __restrict__ cache,
+                              const int* __restrict__ block_table, int table_width, const int* __restrict__ request_of_row,
+                              const int* __restrict__ positions, const int* __restrict__ cu_q, int rows, int heads,
+                              int kv_heads, int dim, int vdim, int page_size, int num_pages, float scale, float lam,
+                              float out_scale, float eps, int window, int splits, int small_rows,
+                              float* __restrict__ partial, uint32_t* __restrict__ error) {
+  extern __shared__ float smem[];
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long unit = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  if (unit >= static_cast<long long>(rows) * heads) return;
+  const int row = static_cast<int>(unit / heads), head = static_cast<int>(unit % heads);
+  const int req = request_of_row[row];
+  if (req < 0) {                                           // a row of padding: zeros, so that nothing unset travels on
+    T* o = out + static_cast<long long>(row) * heads * vdim + static_cast<long long>(head) * vdim;
+    if (blockIdx.y == 0)
+      for (int e = lane; e < vdim; e += 32) o[e] = from_float<T>(0.0f);
+    return;
+  }
+  if (splits > 1 && cu_q[req + 1] - cu_q[req] > small_rows) return;
+  const int g = head / (heads / kv_heads);
+  float* q = smem + warp * 2 * dim;                        // map 1 | map 2
+  const T* qr = qkv + row * ld + static_cast<long long>(head) * 2 * dim;
+  for (int e = lane; e < 2 * dim; e += 32) q[e] = to_float<T>(qr[e]);
+  __syncwarp();
+  const int pos = positions[row];
+  int first = window > 0 ? max(0, pos - window + 1) : 0, last = pos;
+  if (splits > 1) {                                        // equal stretches of whole chunks
+    const int chunk0 = first >> 5, chunks = (pos >> 5) - chunk0 + 1;
+    const int per = (chunks + splits - 1) / splits;
+    const int c_lo = chunk0 + static_cast<int>(blockIdx.y) * per;
+    first = max(first, c_lo << 5);
+    last = min(pos, ((c_lo + per) << 5) - 1);
+  }
+  const int* table = block_table + static_cast<long long>(req) * table_width;
+  float a1[kDiffMaxPerLane], a2[kDiffMaxPerLane];
+#pragma unroll
+  for (int e = 0; e < kDiffMaxPerLane; ++e) a1[e] = a2[e] = 0.0f;
+  float m1 = -INFINITY, m2 = -INFINITY, l1 = 0.0f, l2 = 0.0f;
+  if (first <= last)
+    diff_stretch<T>(q, cache, table, first, last, g, kv_heads, dim, vdim, page_size, num_pages, scale, lane, a1, a2, m1, m2,
+                    l1, l2, error);
+  if (splits > 1) {
+    float* p = partial + ((static_cast<long long>(row) * heads + head) * splits + blockIdx.y) * (4 + 2 * vdim);
+    if (lane == 0) { p[0] = m1; p[1] = l1; p[2] = m2; p[3] = l2; }
+#pragma unroll
+    for (int e = 0; e < kDiffMaxPerLane; ++e)
+      if (lane + 32 * e < vdim) { p[4 + lane + 32 * e] = a1[e]; p[4 + vdim + lane + 32 * e] = a2[e]; }
+    return;
+  }
   if (!(l1 > 0.0f) || !(l2 > 0.0f) || l1 > 3.0e38f || l2 > 3.0e38f) {
     if (lane == 0) publish_error(error, kAttentionDenominator);
     l1 = l2 = 1.0f;
   }
   diff_finish<T>(a1, a2, l1, l2, lam, eps, out_scale, vdim, lane,
                  out + static_cast<long long>(row) * heads * vdim + static_cast<long long>(head) * vdim);
+}
+
+// A warp a (row, head): the parts' sums folded in order, then the combination and the head's norm.
+template <typename T>
+__global__ void __launch_bounds__(128)
+diff_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, const int* __restrict__ request_of_row,
+                            const int* __restrict__ cu_q, int rows, int heads, int vdim, int splits, int small_rows,
+                            float lam, float out_scale, float eps, uint32_t* __restrict__ error) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long unit = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + warp;
+  if (unit >= static_cast<long long>(rows) * heads) return;
+  const int row = static_cast<int>(unit / heads);
+  const int req = request_of_row[row];
+  if (req < 0 || cu_q[req + 1] - cu_q[req] > small_rows) return;
+  float a1[kDiffMaxPerLane], a2[kDiffMaxPerLane];
+#pragma unroll
+  for (int e = 0; e < kDiffMaxPerLane; ++e) a1[e] = a2[e] = 0.0f;
+  float m1 = -INFINITY, m2 = -INFINITY, l1 = 0.0f, l2 = 0.0f;
+  for (int s = 0; s < splits; ++s) {
+    const float* p = partial + (unit * splits + s) * (4 + 2 * vdim);
+    const float pm1 = p[0], pl1 = p[1], pm2 = p[2], pl2 = p[3];
+    if (pm1 == -INFINITY) continue;                         // a part without keys
+    const float n1 = fmaxf(m1, pm1), n2 = fmaxf(m2, pm2);
+    const float c1 = expf(m1 - n1), c2 = expf(m2 - n2), d1 = expf(pm1 - n1), d2 = expf(pm2 - n2);
+    l1 = l1 * c1 + pl1 * d1;
+    l2 = l2 * c2 + pl2 * d2;
+    m1 = n1;
+    m2 = n2;
+#pragma unroll
+    for (int e = 0; e < kDiffMaxPerLane; ++e)
+      if (lane + 32 * e < vdim) {
+        a1[e] = a1[e] * c1 + p[4 + lane + 32 * e] * d1;
+        a2[e] = a2[e] * c2 + p[4 + vdim + lane + 32 * e] * d2;
+      }
+  }
+  if (!(l1 > 0.0f) || !(l2 > 0.0f) || l1 > 3.0e38f || l2 > 3.0e38f) {
+    if (lane == 0) publish_error(error, kAttentionDenominator);
+    l1 = l2 = 1.0f;
+  }
+  diff_finish<T>(a1, a2, l1, l2, lam, eps, out_scale, vdim, lane, out + unit * vdim);
+}
+
+// Tensor cores for requests of more than ``small_rows`` rows (bf16).  A block is 64 consecutive rows of one request and
+// one head (found on the device from cu_q: block x of the grid is the x-th such tile of the step, blocks beyond the
+// last leave), a warp 16 of them.  Key tiles of 64 (both maps' keys and the values of the head's key/value head) come
+// by cp.async into two buffers; columns beyond dim / vdim up to the instance's DIM / VDIM are zeros.  Per map:
+// S = Q K^T (32-bit), the running maximum and sum of a row in the exp2 domain, P as a bf16 pair (rounding, remainder)
+// into O += P V.  At the end o = O1 / l1 - lambda O2 / l2, its norm over vdim, out_scale.
+template <int DIM, int VDIM>
+__global__ void __launch_bounds__(128)
+diff_attention_tile_kernel(const __nv_bfloat16* __restrict__ qkv, long long ld, __nv_bfloat16* __restrict__ out,
+                           const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table, int table_width,
+                           const int* __restrict__ cu_q, const int* __restrict__ q_start, int requests, int heads,
+                           int kv_heads, int dim, int vdim, int page_size, int num_pages, float scale, float lam,
+                           float out_scale, float eps, int window, int small_rows, uint32_t* __restrict__ error) {
+  typedef __nv_bfloat16 bf16;
+  constexpr int QLD = 2 * DIM + 8, VLD = VDIM + 8;           // row strides that keep ldmatrix free of bank conflicts
+  constexpr int QC = 2 * DIM / 8, VC = VDIM / 8, PER = QC + VC;   // 16-byte pieces of a row of q or k, of v, of a key
+  extern __shared__ __align__(16) unsigned char diff_tile_smem[];
+  bf16* Qs = reinterpret_cast<bf16*>(diff_tile_smem);         // [64][QLD]
+  bf16* Ks = Qs + 64 * QLD;                                   // [2][64][QLD]
+  bf16* Vs = Ks + 2 * 64 * QLD;                               // [2][64][VLD]
+  __shared__ int tile_info[2];
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) {
+    int t = blockIdx.x, found = -1, at = 0;
+    for (int r = 0; r < requests; ++r) {
+      const int n = cu_q[r + 1] - cu_q[r];
+      if (n <= small_rows) continue;
+      const int tiles = (n + 63) >> 6;
+      if (t < tiles) { found = r; at = cu_q[r] + t * 64; break; }
+      t -= tiles;
+    }
+    tile_info[0] = found;
+    tile_info[1] = at;
+  }
+  __syncthreads();
+  const int req = tile_info[0];
+  if (req < 0) return;
+  const int row0 = tile_info[1];
+  const int nrows = min(64, cu_q[req + 1] - row0);
+  const int pos0 = q_start[req] + (row0 - cu_q[req]);
+  const int head = blockIdx.y, g = head / (heads / kv_heads);
+  const long long width = static_cast<long long>(kv_heads) * (2 * dim + vdim);
+  const int* table = block_table + static_cast<long long>(req) * table_width;
+  const int key_last = pos0 + nrows - 1;
+  const int key_first = window > 0 ? max(0, pos0 - window + 1) : 0;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+  for (int c = tid; c < 64 * QC; c += 128) {
+    const int rr = c / QC, cc = c % QC, map = cc / (DIM / 8), col = (cc % (DIM / 8)) * 8;
+    bf16* dst = Qs + rr * QLD + map * DIM + col;
+    if (rr < nrows && col < dim)
+      mma::copy_async_16(dst, qkv + (row0 + rr) * ld + static_cast<long long>(head) * 2 * dim + map * dim + col);
+    else
+      *reinterpret_cast<uint4*>(dst) = zero;
+  }
+  auto load_keys = [&](int buf, int j0) {
+    bf16* kb = Ks + buf * 64 * QLD;
+    bf16* vb = Vs + buf * 64 * VLD;
+    for (int c = tid; c < 64 * PER; c += 128) {
+      const int key = c / PER, cc = c % PER, j = j0 + key;
+      long long at = -1;
+      if (j >= key_first && j <= key_last) {
+        const int page = table[j / page_size];
+        if (page < 0 || page >= num_pages) publish_error(error, kRowWithoutPage);
+        else at = (static_cast<long long>(page) * page_size + j % page_size) * width;
+      }
+      if (cc < QC) {
+        const int map = cc / (DIM / 8), col = (cc % (DIM / 8)) * 8;
+        bf16* dst = kb + key * QLD + map * DIM + col;
+        if (at >= 0 && col < dim) mma::copy_async_16(dst, cache + at + static_cast<long long>(g) * 2 * dim + map * dim + col);
+        else *reinterpret_cast<uint4*>(dst) = zero;
+      } else {
+        const int col = (cc - QC) * 8;
+        bf16* dst = vb + key * VLD + col;
+        if (at >= 0 && col < vdim)
+          mma::copy_async_16(dst, cache + at + static_cast<long long>(kv_heads) * 2 * dim + static_cast<long long>(g) * vdim + col);
+        else
+          *reinterpret_cast<uint4*>(dst) = zero;
+      }
+    }
+    mma::copy_async_commit();
+  };
+  const int tile_lo = key_first >> 6, tile_hi = key_last >> 6;
+  load_keys(0, tile_lo * 64);                                 // (the group also holds the copies of q)
+
+  const int wr0 = warp * 16;
+  const int ra = wr0 + (lane >> 2), rb = ra + 8;
+  const int pos_a = ra < nrows ? pos0 + ra : -1, pos_b = rb < nrows ? pos0 + rb : -1;
+  const int warp_last = pos0 + min(wr0 + 15, nrows - 1);
+  const float to_exp2 = scale * 1.4426950408889634f;
+  float O[2][VDIM / 8][4];
+  float m[2][2], l[2][2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    m[j][0] = m[j][1] = -INFINITY;
+    l[j][0] = l[j][1] = 0.0f;
+#pragma unroll
+    for (int n = 0; n < VDIM / 8; ++n) O[j][n][0] = O[j][n][1] = O[j][n][2] = O[j][n][3] = 0.0f;
+  }
+  for (int it = tile_lo; it <= tile_hi; ++it) {
+    const int buf = (it - tile_lo) & 1;
+    if (it < tile_hi) {
+      load_keys(buf ^ 1, (it + 1) * 64);
+      mma::copy_async_wait<1>();
+    } else {
+      mma::copy_async_wait<0>();
+    }
+    __syncthreads();
+    const int j0 = it * 64;
+    if (wr0 < nrows && j0 <= warp_last) {
+      const bf16* kb = Ks + buf * 64 * QLD;
+      const bf16* vb = Vs + buf * 64 * VLD;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        float S[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) S[n][0] = S[n][1] = S[n][2] = S[n][3] = 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < DIM / 16; ++kk) {
+          uint32_t a[4];
+          mma::load_matrices(a, Qs + (wr0 + (lane & 15)) * QLD + j * DIM + kk * 16 + (lane >> 4) * 8);
+#pragma unroll
+          for (int np = 0; np < 4; ++np) {
+            uint32_t b[4];
+            mma::load_matrices(b, kb + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * QLD + j * DIM + kk * 16 + ((lane >> 3) & 1) * 8);
+            mma::multiply_add(S[2 * np], a, b[0], b[1]);
+            mma::multiply_add(S[2 * np + 1], a, b[2], b[3]);
+          }
+        }
+        float top_a = -INFINITY, top_b = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int key = j0 + n * 8 + 2 * (lane & 3) + c;
+            const bool see_a = key <= pos_a && (window <= 0 || key > pos_a - window);
+            const bool see_b = key <= pos_b && (window <= 0 || key > pos_b - window);
+            S[n][c] = see_a ? S[n][c] * to_exp2 : -INFINITY;
+            S[n][2 + c] = see_b ? S[n][2 + c] * to_exp2 : -INFINITY;
+            top_a = fmaxf(top_a, S[n][c]);
+            top_b = fmaxf(top_b, S[n][2 + c]);
+          }
+        }
+        top_a = fmaxf(top_a, __shfl_xor_sync(0xffffffffu, top_a, 1));
+        top_a = fmaxf(top_a, __shfl_xor_sync(0xffffffffu, top_a, 2));
+        top_b = fmaxf(top_b, __shfl_xor_sync(0xffffffffu, top_b, 1));
+        top_b = fmaxf(top_b, __shfl_xor_sync(0xffffffffu, top_b, 2));
+        const float new_a = fmaxf(m[j][0], top_a), new_b = fmaxf(m[j][1], top_b);
+        const float ref_a = new_a == -INFINITY ? 0.0f : new_a, ref_b = new_b == -INFINITY ? 0.0f : new_b;
+        const float fix_a = exp2f(m[j][0] - ref_a), fix_b = exp2f(m[j][1] - ref_b);
+        m[j][0] = new_a;
+        m[j][1] = new_b;
+        float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          S[n][0] = exp2f(S[n][0] - ref_a);
+          S[n][1] = exp2f(S[n][1] - ref_a);
+          S[n][2] = exp2f(S[n][2] - ref_b);
+          S[n][3] = exp2f(S[n][3] - ref_b);
+          sum_a += S[n][0] + S[n][1];
+          sum_b += S[n][2] + S[n][3];
+        }
+        l[j][0] = fmaf(l[j][0], fix_a, sum_a);
+        l[j][1] = fmaf(l[j][1], fix_b, sum_b);
+#pragma unroll
+        for (int n = 0; n < VDIM / 8; ++n) {
+          O[j][n][0] *= fix_a;
+          O[j][n][1] *= fix_a;
+          O[j][n][2] *= fix_b;
+          O[j][n][3] *= fix_b;
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {                      // 16 keys a step
+          uint32_t hi[4], lo[4];
+          hi[0] = mma::pack(S[2 * kk][0], S[2 * kk][1]);
+          hi[1] = mma::pack(S[2 * kk][2], S[2 * kk][3]);
+          hi[2] = mma::pack(S[2 * kk + 1][0], S[2 * kk + 1][1]);
+          hi[3] = mma::pack(S[2 * kk + 1][2], S[2 * kk + 1][3]);
+          lo[0] = mma::pack_remainder(S[2 * kk][0], S[2 * kk][1]);
+          lo[1] = mma::pack_remainder(S[2 * kk][2], S[2 * kk][3]);
+          lo[2] = mma::pack_remainder(S[2 * kk + 1][0], S[2 * kk + 1][1]);
+          lo[3] = mma::pack_remainder(S[2 * kk + 1][2], S[2 * kk + 1][3]);
+#pragma unroll
+          for (int vp = 0; vp < VDIM / 16; ++vp) {
+            uint32_t b[4];
+            mma::load_matrices_transposed(b, vb + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * VLD + vp * 16 + (lane >> 4) * 8);
+            mma::multiply_add(O[j][2 * vp], hi, b[0], b[1]);
+            mma::multiply_add(O[j][2 * vp + 1], hi, b[2], b[3]);
+            mma::multiply_add(O[j][2 * vp], lo, b[0], b[1]);
+            mma::multiply_add(O[j][2 * vp + 1], lo, b[2], b[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (wr0 >= nrows) return;
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      l[j][r] += __shfl_xor_sync(0xffffffffu, l[j][r], 1);
+      l[j][r] += __shfl_xor_sync(0xffffffffu, l[j][r], 2);
+    }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int row = r == 0 ? ra : rb;
+    const bool valid = row < nrows;                            // (the shuffles below are the whole warp's)
+    float l1 = l[0][r], l2 = l[1][r];
+    if (valid && (!(l1 > 0.0f) || !(l2 > 0.0f) || l1 > 3.0e38f || l2 > 3.0e38f)) publish_error(error, kAttentionDenominator);
+    if (!(l1 > 0.0f)) l1 = 1.0f;
+    if (!(l2 > 0.0f)) l2 = 1.0f;
+    const float i1 = 1.0f / l1, i2 = 1.0f / l2;
+    float ss = 0.0f;
+#pragma unroll
+    for (int n = 0; n < VDIM / 8; ++n)
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float o = O[0][n][2 * r + c] * i1 - lam * (O[1][n][2 * r + c] * i2);
+        O[0][n][2 * r + c] = o;                                // (columns beyond vdim are zeros)
+        ss = fmaf(o, o, ss);
+      }
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    const float inv = out_scale / sqrtf(ss / static_cast<float>(vdim) + eps);
+    if (!valid) continue;
+    bf16* o = out + (static_cast<long long>(row0 + row) * heads + head) * vdim;
+#pragma unroll
+    for (int n = 0; n < VDIM / 8; ++n) {
+      const int col = n * 8 + 2 * (lane & 3);
+      if (col < vdim)                                          // vdim is a multiple of 8: the pair is inside
+        *reinterpret_cast<__nv_bfloat162*>(o + col) = __floats2bfloat162_rn(O[0][n][2 * r] * inv, O[0][n][2 * r + 1] * inv);
+    }
+  }
 }
 
 }  // namespace pih
@@ -210,22 +531,76 @@ extern "C" int pih_diff_qk_prepare(int dtype, void* qkv, long long ld, const voi
   return 0;
 }
 
-extern "C" int pih_diff_attention_generic(int dtype, const void* qkv, long long ld, void* out, const void* cache,
-                                          const void* block_table, int table_width, const void* request_of_row,
-                                          const void* positions, int rows, int heads, int kv_heads, int dim, int vdim,
-                                          int page_size, int num_pages, float scale, float lam, float out_scale, float eps,
-                                          int window, void* error, void* stream) {
+template <int DIM, int VDIM>
+static int launch_diff_tile(cudaStream_t s, unsigned tiles, const void* qkv, long long ld, void* out, const void* cache,
+                            const void* block_table, int table_width, const void* cu_q, const void* q_start, int requests,
+                            int heads, int kv_heads, int dim, int vdim, int page_size, int num_pages, float scale, float lam,
+                            float out_scale, float eps, int window, int small_rows, void* error) {
+  const size_t smem = (static_cast<size_t>(3) * 64 * (2 * DIM + 8) + 2 * 64 * (VDIM + 8)) * sizeof(bf16);
+  static bool raised = false;
+  if (!raised && smem > 48 * 1024) {
+    cudaFuncSetAttribute(diff_attention_tile_kernel<DIM, VDIM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(smem));
+    raised = true;
+  }
+  launch_kernel(diff_attention_tile_kernel<DIM, VDIM>, dim3(tiles, heads), dim3(128), smem, s, static_cast<const bf16*>(qkv),
+                ld, static_cast<bf16*>(out), static_cast<const bf16*>(cache), static_cast<const int*>(block_table),
+                table_width, static_cast<const int*>(cu_q), static_cast<const int*>(q_start), requests, heads, kv_heads, dim,
+                vdim, page_size, num_pages, scale, lam, out_scale, eps, window, small_rows, static_cast<uint32_t*>(error));
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+// 1 when the tensor-core kernel has an instance for these sizes (bf16; dim and vdim multiples of 8 up to 128).
+extern "C" int pih_diff_attention_tile_takes(int dim, int vdim) {
+  return dim >= 8 && vdim >= 8 && dim % 8 == 0 && vdim % 8 == 0 && dim <= 128 && vdim <= 128;
+}
+
+// The attention of the step's rows.  ``tile`` (bf16 only, sizes that pih_diff_attention_tile_takes): requests of more
+// than 16 rows run on the tensor-core kernel.  ``small``: the other rows (all rows without ``tile``) run on the warp
+// kernel, their keys cut into ``splits`` parts (1: uncut, the row's result does not depend on the step's make-up by a
+// bit) through ``partial`` (fp32 [rows, heads, splits, 4 + 2 vdim]).
+extern "C" int pih_diff_attention(int dtype, const void* qkv, long long ld, void* out, const void* cache,
+                                  const void* block_table, int table_width, const void* request_of_row,
+                                  const void* positions, const void* cu_q, const void* q_start, int rows, int requests,
+                                  int heads, int kv_heads, int dim, int vdim, int page_size, int num_pages, float scale,
+                                  float lam, float out_scale, float eps, int window, int tile, int small, int splits,
+                                  void* partial, void* error, void* stream) {
   if (rows <= 0) return 0;
-  if (dim > 32 * kDiffMaxPerLane * 4 || vdim > 32 * kDiffMaxPerLane || heads % kv_heads) return PIH_ERR_UNSUPPORTED;
+  if (dim > 32 * kDiffMaxPerLane * 4 || vdim > 32 * kDiffMaxPerLane || heads % kv_heads || splits < 1) return PIH_ERR_UNSUPPORTED;
+  if (tile && (dtype != PIH_BF16 || !pih_diff_attention_tile_takes(dim, vdim) || ld % 8)) return PIH_ERR_UNSUPPORTED;
+  if (splits > 1 && partial == nullptr) return PIH_ERR_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int small_rows = tile ? 16 : 0x7fffffff;
+  if (tile) {
+    const unsigned tiles = static_cast<unsigned>((rows + 63) / 64 + requests);
+    int rc;
+#define PIH_TILE(D, V)                                                                                                 \
+  rc = launch_diff_tile<D, V>(s, tiles, qkv, ld, out, cache, block_table, table_width, cu_q, q_start, requests, heads, \
+                              kv_heads, dim, vdim, page_size, num_pages, scale, lam, out_scale, eps, window, small_rows, error)
+    if (dim <= 32) { if (vdim <= 64) PIH_TILE(32, 64); else PIH_TILE(32, 128); }
+    else if (dim <= 64) { if (vdim <= 64) PIH_TILE(64, 64); else PIH_TILE(64, 128); }
+    else { if (vdim <= 64) PIH_TILE(128, 64); else PIH_TILE(128, 128); }
+#undef PIH_TILE
+    if (rc != 0) return rc;
+  }
+  if (!small) return 0;
   const long long units = static_cast<long long>(rows) * heads;
   const size_t smem = 4 * 2 * static_cast<size_t>(dim) * sizeof(float);
+  const dim3 grid(static_cast<unsigned>((units + 3) / 4), splits);
 #define PIH_DAG(T)                                                                                                     \
-  launch_kernel(diff_attention_generic_kernel<T>, dim3(static_cast<unsigned>((units + 3) / 4)), dim3(128), smem, s,    \
-                static_cast<const T*>(qkv), ld, static_cast<T*>(out), static_cast<const T*>(cache),                    \
-                static_cast<const int*>(block_table), table_width, static_cast<const int*>(request_of_row),            \
-                static_cast<const int*>(positions), rows, heads, kv_heads, dim, vdim, page_size, num_pages, scale, lam, \
-                out_scale, eps, window, static_cast<uint32_t*>(error))
+  do {                                                                                                                 \
+    launch_kernel(diff_attention_generic_kernel<T>, grid, dim3(128), smem, s, static_cast<const T*>(qkv), ld,          \
+                  static_cast<T*>(out), static_cast<const T*>(cache), static_cast<const int*>(block_table), table_width, \
+                  static_cast<const int*>(request_of_row), static_cast<const int*>(positions),                         \
+                  static_cast<const int*>(cu_q), rows, heads, kv_heads, dim, vdim, page_size, num_pages, scale, lam,   \
+                  out_scale, eps, window, splits, small_rows, static_cast<float*>(partial), static_cast<uint32_t*>(error)); \
+    PIH_LAUNCH_CHECK();                                                                                                \
+    if (splits > 1)                                                                                                    \
+      launch_kernel(diff_attention_merge_kernel<T>, dim3(grid.x), dim3(128), 0, s, static_cast<const float*>(partial), \
+                    static_cast<T*>(out), static_cast<const int*>(request_of_row), static_cast<const int*>(cu_q), rows, \
+                    heads, vdim, splits, small_rows, lam, out_scale, eps, static_cast<uint32_t*>(error));              \
+  } while (0)
   if (dtype == PIH_F32) PIH_DAG(float);
   else if (dtype == PIH_BF16) PIH_DAG(bf16);
   else return PIH_ERR_BAD_ARGUMENT;

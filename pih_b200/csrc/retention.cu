@@ -2,7 +2,8 @@
 //
 //   retention_prepare      q and k of every row rotated by the row's position (angles formed in 32-bit from the
 //                          frequencies), k then scaled: 32-bit copies [rows, heads, dim]
-//   retention_recurrence   per token  S <- S + (decay - 1) S + k v^T,  o = S^T q,  from the request's state slot
+//   retention_recurrence   per token  S <- S + (decay - 1) S + k v^T,  o = S^T q,  from the request's state slot; S in
+//                          shared memory (any key size), or in registers for the key sizes that have an instance
 //
 // The order of the additions of a read-out is fixed by the kernel: it does not depend on how a sequence is cut into
 // steps or on what else a step holds.
@@ -118,6 +119,103 @@ __global__ void retention_recurrence_kernel(const float* __restrict__ qf, const 
     for (int i = 0; i < dim; ++i) Sg[static_cast<long long>(i) * vdim + col] = S[i * cols + j];
 }
 
+// The same recurrence with S in registers, for the key sizes that have an instance.  Block (request, head, 32 value
+// columns); a column of S is held by kParts threads (thread (column c = tid / kParts, part p = tid % kParts) the rows
+// p * kDim / kParts ...), so the parts of a column sit in neighbouring lanes and meet through shuffles.  What the
+// recurrence reads of a token (k, q, the block's 32 values) is staged in shared memory a chunk of tokens at a time, two
+// buffers: the next chunk's numbers are copied asynchronously while this chunk is computed, so no load from memory
+// and only one barrier a chunk lie on the chain from token to token.  The order of the additions is fixed by the
+// kernel, not by the step's make-up or by where a chunk begins.
+__device__ __forceinline__ void retention_copy_16(void* smem_dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(src));
+}
+
+template <typename T, int kDim>
+__global__ void __launch_bounds__(kDim >= 64 ? 256 : (kDim >= 32 ? 128 : 64))
+retention_recurrence_reg_kernel(const float* __restrict__ qf, const float* __restrict__ kf, const T* __restrict__ v,
+                                long long ldv, const float* __restrict__ decay_m1, float* __restrict__ out,
+                                float* __restrict__ state, long long state_stride, const int* __restrict__ cu_q,
+                                const int* __restrict__ state_slots, int heads, int vdim) {
+  constexpr int kParts = kDim >= 64 ? 8 : (kDim >= 32 ? 4 : 2);   // threads a column of S
+  constexpr int kThreads = 32 * kParts;
+  constexpr int kRows = kDim / kParts;                    // rows of S a thread holds (a multiple of 4)
+  constexpr int kSeg = kRows + 4;                         // a part's stretch of k (or q) in the staging buffer: the parts'
+                                                          // 16-byte reads fall into different banks
+  constexpr int kChunk = kDim <= 128 ? 16 : 8;            // tokens staged at a time
+  constexpr int kVWords = 32 * sizeof(T) / 4;             // the block's 32 values of a token, in 32-bit words
+  constexpr int kTok = 2 * kParts * kSeg + kVWords;       // words staged a token: k | q | values
+  constexpr int kCopies = 2 * (kDim / 4) + kVWords / 4;   // 16-byte copies a token
+  extern __shared__ __align__(16) float stage[];          // [2][kChunk][kTok]
+  wait_for_prior_kernels();
+  launch_dependents();
+  const int r = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * 32;
+  const int lo = cu_q[r], hi = cu_q[r + 1];
+  const int slot = state_slots[r];
+  if (hi <= lo || slot < 0) return;
+  const int tid = threadIdx.x, c = tid / kParts, p = tid % kParts;
+  float* Sg = state + slot * state_stride + (static_cast<long long>(h) * kDim + p * kRows) * vdim + col0 + c;
+  float S[kRows];
+#pragma unroll
+  for (int i = 0; i < kRows; ++i) S[i] = Sg[static_cast<long long>(i) * vdim];
+  const float dm1 = decay_m1[h];
+  auto fetch = [&](int buf, int t0) {
+    const int n = min(kChunk, hi - t0);
+    for (int e = tid; e < n * kCopies; e += kThreads) {
+      const int tok = e / kCopies, piece = e % kCopies;
+      float* dst = stage + (buf * kChunk + tok) * kTok;
+      const long long t = t0 + tok;
+      if (piece < 2 * (kDim / 4)) {
+        const int which = piece / (kDim / 4), at = (piece % (kDim / 4)) * 4;       // k or q; the element
+        const float* src = (which == 0 ? kf : qf) + (t * heads + h) * kDim + at;
+        retention_copy_16(dst + which * kParts * kSeg + (at / kRows) * kSeg + at % kRows, src);
+      } else {
+        const int w = piece - 2 * (kDim / 4);
+        retention_copy_16(dst + 2 * kParts * kSeg + w * 4,
+                          reinterpret_cast<const float*>(v + t * ldv + static_cast<long long>(h) * vdim + col0) + w * 4);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  fetch(0, lo);
+  int buf = 0;
+  for (int t0 = lo; t0 < hi; t0 += kChunk, buf ^= 1) {
+    if (t0 + kChunk < hi) {
+      fetch(buf ^ 1, t0 + kChunk);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const int n = min(kChunk, hi - t0);
+    for (int tok = 0; tok < n; ++tok) {
+      const float* cur = stage + (buf * kChunk + tok) * kTok;
+      const float4* k4 = reinterpret_cast<const float4*>(cur + p * kSeg);
+      const float4* q4 = reinterpret_cast<const float4*>(cur + kParts * kSeg + p * kSeg);
+      const float vj = to_float<T>(reinterpret_cast<const T*>(cur + 2 * kParts * kSeg)[c]);
+      float o0 = 0.0f, o1 = 0.0f, o2 = 0.0f, o3 = 0.0f;
+#pragma unroll
+      for (int i = 0; i < kRows / 4; ++i) {
+        const float4 k = k4[i], q = q4[i];
+        S[4 * i + 0] = fmaf(k.x, vj, fmaf(dm1, S[4 * i + 0], S[4 * i + 0]));
+        S[4 * i + 1] = fmaf(k.y, vj, fmaf(dm1, S[4 * i + 1], S[4 * i + 1]));
+        S[4 * i + 2] = fmaf(k.z, vj, fmaf(dm1, S[4 * i + 2], S[4 * i + 2]));
+        S[4 * i + 3] = fmaf(k.w, vj, fmaf(dm1, S[4 * i + 3], S[4 * i + 3]));
+        o0 = fmaf(S[4 * i + 0], q.x, o0);
+        o1 = fmaf(S[4 * i + 1], q.y, o1);
+        o2 = fmaf(S[4 * i + 2], q.z, o2);
+        o3 = fmaf(S[4 * i + 3], q.w, o3);
+      }
+      float o = (o0 + o1) + (o2 + o3);
+#pragma unroll
+      for (int d = 1; d < kParts; d <<= 1) o += __shfl_xor_sync(0xffffffffu, o, d);
+      if (p == 0) out[((static_cast<long long>(t0) + tok) * heads + h) * vdim + col0 + c] = o;
+    }
+    __syncthreads();                                       // the buffer is free for the chunk after the next
+  }
+#pragma unroll
+  for (int i = 0; i < kRows; ++i) Sg[static_cast<long long>(i) * vdim] = S[i];
+}
+
 }  // namespace pih
 
 using namespace pih;
@@ -141,12 +239,29 @@ extern "C" int pih_retention(int dtype, const void* qk, long long ld, const void
   float* kf = qf + static_cast<long long>(rows) * heads * dim;
   const long long n = static_cast<long long>(rows) * heads * dim;
   const dim3 grid(requests, heads, (vdim + cols - 1) / cols);
+  // S in registers: the key sizes with an instance, value columns in whole slabs of 32, and everything that is copied
+  // in 16-byte pieces on a 16-byte boundary
+  const size_t esize = dtype == PIH_F32 ? 4 : 2;
+  const bool in_registers = (dim == 16 || dim == 32 || dim == 64 || dim == 128 || dim == 256) && vdim % 32 == 0 &&
+                            (reinterpret_cast<uintptr_t>(v) % 16 == 0) && (ldv * esize) % 16 == 0 &&
+                            (vdim * esize) % 16 == 0 && (reinterpret_cast<uintptr_t>(scratch) % 16 == 0);
+#define PIH_RET_REG(T, D)                                                                                                do {                                                                                                                     constexpr int parts = D >= 64 ? 8 : (D >= 32 ? 4 : 2);                                                                 constexpr int chunk = D <= 128 ? 16 : 8;                                                                               constexpr size_t bytes = 2 * chunk * (2 * parts * (D / parts + 4) + 32 * sizeof(T) / 4) * sizeof(float);               if (bytes > 48 * 1024)                                                                                                   cudaFuncSetAttribute(retention_recurrence_reg_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,                                    static_cast<int>(bytes));                                                                       launch_kernel(retention_recurrence_reg_kernel<T, D>, dim3(requests, heads, vdim / 32), dim3(32 * parts), bytes, s,                   static_cast<const float*>(qf), static_cast<const float*>(kf), static_cast<const T*>(v), ldv,                           static_cast<const float*>(decay_m1), static_cast<float*>(out), static_cast<float*>(state),                             state_stride, static_cast<const int*>(cu_q), static_cast<const int*>(state_slots), heads, vdim);       } while (0)
 #define PIH_RET(T)                                                                                                     \
   do {                                                                                                                 \
     launch_kernel(retention_prepare_kernel<T>, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s,          \
                   static_cast<const T*>(qk), ld, static_cast<const float*>(freq), static_cast<const int*>(positions),  \
                   qf, kf, rows, heads, dim, rot, key_scale);                                                           \
     PIH_LAUNCH_CHECK();                                                                                                \
+    if (in_registers) {                                                                                                \
+      switch (dim) {                                                                                                   \
+        case 16: PIH_RET_REG(T, 16); break;                                                                            \
+        case 32: PIH_RET_REG(T, 32); break;                                                                            \
+        case 64: PIH_RET_REG(T, 64); break;                                                                            \
+        case 128: PIH_RET_REG(T, 128); break;                                                                          \
+        default: PIH_RET_REG(T, 256); break;                                                                           \
+      }                                                                                                                \
+      break;                                                                                                           \
+    }                                                                                                                  \
     if (smem > 48 * 1024)                                                                                              \
       cudaFuncSetAttribute(retention_recurrence_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,                \
                            static_cast<int>(smem));                                                                    \
@@ -159,6 +274,7 @@ extern "C" int pih_retention(int dtype, const void* qk, long long ld, const void
   else if (dtype == PIH_BF16) PIH_RET(bf16);
   else return PIH_ERR_BAD_ARGUMENT;
 #undef PIH_RET
+#undef PIH_RET_REG
   PIH_LAUNCH_CHECK();
   return 0;
 }

@@ -109,7 +109,7 @@ class CudaOps:
                      "pih_gated_delta_rule", "pih_gated_rmsnorm", "pih_rglru_scan", "pih_latent_write",
                      "pih_latent_attention_generic", "pih_moe_route", "pih_moe_experts", "pih_moe_combine_bf16", "pih_latent_attention_split", "pih_latent_attention_splits", "pih_latent_attention_mma", "pih_batched_gemv",
                      "pih_stream_cast", "pih_stream_norm_add", "pih_bias_xielu", "pih_add_gated", "pih_retention",
-                     "pih_diff_qk_prepare", "pih_diff_attention_generic", "pih_moe_route_scored"):
+                     "pih_diff_qk_prepare", "pih_diff_attention", "pih_diff_attention_tile_takes", "pih_moe_route_scored"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
         lib.pih_top_logprobs_scratch_words.restype = c_ll
@@ -929,13 +929,37 @@ class CudaOps:
                        value_dim: int) -> torch.Tensor:
         """Differential attention of the step's rows (their q maps, prepared, in the first columns of ``qkv``) over the
         cache: per head ``softmax_1 v - lam * softmax_2 v``, divided by its root mean square (``norm_eps``) and times
-        ``out_scale``.  Returns ``[T, heads * value_dim]`` in the compute dtype."""
+        ``out_scale``.  Returns ``[T, heads * value_dim]`` in the compute dtype.
+
+        32-bit: a warp a (row, head) over the row's keys in a fixed order (the result does not depend on the step's
+        make-up).  bf16: requests of more than 16 rows on the tensor-core kernel when it has an instance for the
+        sizes, the other rows on the warp kernel with their keys cut into parts that run side by side."""
         rows = qkv.shape[0]
         num_pages, page_size = cache.shape[0], cache.shape[1]
         out = torch.empty(rows, heads * value_dim, dtype=qkv.dtype, device=qkv.device)
-        rc = self.lib.pih_diff_attention_generic(
+        tile, small, splits, partial = 0, 1, 1, None
+        if qkv.dtype == torch.bfloat16 and self.diff_attention_fast:
+            plans = getattr(step, "attention_plans", None)
+            plan = plans[1] if plans is not None and 1 in plans else None
+            if plan is None:
+                plan = self.attention_plan(step.host_cu_q, step.host_q_start, 1)
+                if plans is not None:
+                    plans[1] = plan
+            if self.lib.pih_diff_attention_tile_takes(key_dim, value_dim) and qkv.stride(0) % 8 == 0 and cache.shape[2] % 8 == 0:
+                tile, small = (1 if plan[0] > 0 else 0), (1 if plan[1] > 0 else 0)
+            if small:
+                # the rows of small requests: as many parts as bring the warps of the GPU to work
+                splits = max(1, min(32, (148 * 16) // max(1, rows * heads)))
+                if splits > 1:
+                    partial = torch.empty(rows * heads * splits * (4 + 2 * value_dim), dtype=torch.float32, device=qkv.device)
+        rc = self.lib.pih_diff_attention(
             _DT[qkv.dtype], _ptr(qkv), c_ll(qkv.stride(0)), _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1],
-            _ptr(step.request_of_row), _ptr(step.positions), rows, heads, kv_heads, key_dim, value_dim, page_size, num_pages,
-            c_float(scale), c_float(lam), c_float(out_scale), c_float(norm_eps), int(window), self._err(), self._stream())
-        self._check(rc, "diff_attention_generic")
+            _ptr(step.request_of_row), _ptr(step.positions), _ptr(step.cu_q), _ptr(getattr(step, "q_start", None)), rows,
+            step.num_requests, heads, kv_heads, key_dim, value_dim, page_size, num_pages, c_float(scale), c_float(lam),
+            c_float(out_scale), c_float(norm_eps), int(window), tile, small, splits, _ptr(partial), self._err(),
+            self._stream())
+        self._check(rc, "diff_attention")
+        self.launches += tile + (1 if splits > 1 else 0) + small - 1
         return out
+
+    diff_attention_fast = True             # False: bf16 steps use the in-order warp kernel too

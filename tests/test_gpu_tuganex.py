@@ -216,7 +216,7 @@ def _step(positions, request_of_row, cu_q, slots):
     t = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
     return SimpleNamespace(positions=t(positions), request_of_row=t(request_of_row), cu_q=t(cu_q), state_slots=t(slots),
                            num_requests=len(slots), host_cu_q=list(cu_q), host_q_start=[positions[c] for c in cu_q[:-1]],
-                           meta=None, attention_plans={})
+                           q_start=t([positions[c] for c in cu_q[:-1]]), meta=None, attention_plans={})
 
 
 def _plain_diff_row(q, K, V, scale, lam, eps, out_scale, group):
@@ -241,8 +241,9 @@ def _paged(K, V, page, dtype, pages=None):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("dim, vdim, heads, kv_heads", [(16, 24, 4, 2), (64, 64, 2, 1), (32, 128, 6, 6)])
-@pytest.mark.parametrize("needle", [0, 1, 15, 16, 17, 250, 299])
+@pytest.mark.parametrize("dim, vdim, heads, kv_heads", [(16, 24, 4, 2), (64, 64, 2, 1), (32, 128, 6, 6), (128, 128, 2, 1),
+                                                        (24, 40, 2, 2), (12, 20, 3, 1)])
+@pytest.mark.parametrize("needle", [0, 1, 15, 16, 17, 63, 64, 250, 299])
 def test_differential_attention_finds_one_key_among_hundreds(needle, dim, vdim, heads, kv_heads, dtype):
     """300 cached keys of which ONE matches the query's first map (its score stands out by construction) and another
     one the second map: the first tokens, both sides of a page border, far back, and the row itself — as a single
@@ -329,6 +330,38 @@ def test_differential_attention_portions_of_several_requests(dtype):
         ref = _plain_diff_row(q[t], Ks[r][:p + 1], Vs[r][:p + 1], 0.3, -0.4, 1e-5, 0.8, heads // kv_heads)
         worst = max(worst, float((got[t].view(heads, vdim) - ref).abs().max()) / float(ref.abs().max()))
     assert worst < (1e-5 if dtype == torch.float32 else 2e-2), worst
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_differential_attention_window_edges(dtype):
+    """A window whose oldest key is the standing-out key, and one that has just moved past it: as a decoded row (whole
+    and cut into parts) and as the last row of a portion (the tensor-core kernel in bfloat16)."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(1)
+    heads, kv_heads, dim, vdim, n, page, rows = 2, 1, 16, 32, 200, 8, 40
+    needle, last = 131, n - 1
+    K = torch.randn(n, kv_heads, 2, dim, generator=g, dtype=F64) * 0.3
+    V = torch.randn(n, kv_heads, vdim, generator=g, dtype=F64)
+    q = torch.randn(rows, heads, 2, dim, generator=g, dtype=F64) * 0.1
+    q[-1, :, 0] += 6.0 * K[needle, 0, 0]
+    K, V, q = K.to(dtype).double(), V.to(dtype).double(), q.to(dtype).double()
+    cache, table = _paged(K, V, page, dtype)
+    geometry = dict(heads=heads, kv_heads=kv_heads, key_dim=dim, value_dim=vdim)
+    results = {}
+    for window in (last - needle + 1, last - needle):
+        ref = _plain_diff_row(q[-1], K[last - window + 1:], V[last - window + 1:], 1.0, 0.3, 1e-5, 0.5, heads)
+        one = ops.diff_attention(q[-1:].reshape(1, -1).to(dtype).to(DEV).contiguous(), cache=cache, block_table=table,
+                                 step=_step([last], [0], [0, 1], [0]), scale=1.0, lam=0.3, out_scale=0.5, norm_eps=1e-5,
+                                 window=window, **geometry)[0]
+        many = ops.diff_attention(q.reshape(rows, -1).to(dtype).to(DEV).contiguous(), cache=cache, block_table=table,
+                                  step=_step(list(range(n - rows, n)), [0] * rows, [0, rows], [0]), scale=1.0, lam=0.3,
+                                  out_scale=0.5, norm_eps=1e-5, window=window, **geometry)[-1]
+        ops.check_errors()
+        tol = 1e-5 if dtype == torch.float32 else 2e-2
+        for got in (one, many):
+            assert float((got.double().cpu().view(heads, vdim) - ref).abs().max()) < tol * float(ref.abs().max()), window
+        results[window] = one.double().cpu()
+    assert float((results[last - needle + 1] - results[last - needle]).abs().max()) > 0.1
 
 
 def test_queries_and_keys_are_normed_then_rotated_into_their_slots():
