@@ -187,6 +187,7 @@ retention_recurrence_reg_kernel(const float* __restrict__ qf, const float* __res
     }
     __syncthreads();
     const int n = min(kChunk, hi - t0);
+#pragma unroll 4                                           // (a token's shuffles and store run under the next tokens' FMAs)
     for (int tok = 0; tok < n; ++tok) {
       const float* cur = stage + (buf * kChunk + tok) * kTok;
       const float4* k4 = reinterpret_cast<const float4*>(cur + p * kSeg);
@@ -221,6 +222,26 @@ retention_recurrence_reg_kernel(const float* __restrict__ qf, const float* __res
 using namespace pih;
 typedef __nv_bfloat16 bf16;
 
+template <typename T, int D>
+static void launch_retention_in_registers(cudaStream_t s, const float* qf, const float* kf, const void* v, long long ldv,
+                                          const void* decay_m1, void* out, void* state, long long state_stride,
+                                          const void* cu_q, const void* state_slots, int requests, int heads, int vdim) {
+  constexpr int parts = D >= 64 ? 8 : (D >= 32 ? 4 : 2);
+  constexpr int chunk = D <= 128 ? 16 : 8;
+  constexpr size_t needed = 2 * chunk * (2 * parts * (D / parts + 4) + 32 * sizeof(T) / 4) * sizeof(float);
+  // The token loop is bound by the SM's shared-memory reads: two blocks on one SM each run at half speed.  With fewer
+  // blocks than SMs, every block asks for more than half of an SM's shared memory and so gets an SM alone.
+  const bool alone = static_cast<long long>(requests) * heads * (vdim / 32) <= 148;
+  const size_t bytes = alone && needed < 116 * 1024 ? 116 * 1024 : needed;
+  if (bytes > 48 * 1024)
+    cudaFuncSetAttribute(retention_recurrence_reg_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(bytes));
+  launch_kernel(retention_recurrence_reg_kernel<T, D>, dim3(requests, heads, vdim / 32), dim3(32 * parts), bytes, s, qf, kf,
+                static_cast<const T*>(v), ldv, static_cast<const float*>(decay_m1), static_cast<float*>(out),
+                static_cast<float*>(state), state_stride, static_cast<const int*>(cu_q),
+                static_cast<const int*>(state_slots), heads, vdim);
+}
+
 // qk [rows, ld]: q heads then k heads ([heads, dim] each); v [rows, ldv]: [heads, vdim]; freq fp32 [rot / 2] (null: no
 // rotation); decay_m1 fp32 [heads]: decay - 1; scratch fp32 [2 * rows * heads * dim]; out fp32 [rows, heads, vdim];
 // state fp32: S of (slot, head) at state + slot * state_stride + head * dim * vdim, [dim, vdim].
@@ -245,7 +266,7 @@ extern "C" int pih_retention(int dtype, const void* qk, long long ld, const void
   const bool in_registers = (dim == 16 || dim == 32 || dim == 64 || dim == 128 || dim == 256) && vdim % 32 == 0 &&
                             (reinterpret_cast<uintptr_t>(v) % 16 == 0) && (ldv * esize) % 16 == 0 &&
                             (vdim * esize) % 16 == 0 && (reinterpret_cast<uintptr_t>(scratch) % 16 == 0);
-#define PIH_RET_REG(T, D)                                                                                                do {                                                                                                                     constexpr int parts = D >= 64 ? 8 : (D >= 32 ? 4 : 2);                                                                 constexpr int chunk = D <= 128 ? 16 : 8;                                                                               constexpr size_t bytes = 2 * chunk * (2 * parts * (D / parts + 4) + 32 * sizeof(T) / 4) * sizeof(float);               if (bytes > 48 * 1024)                                                                                                   cudaFuncSetAttribute(retention_recurrence_reg_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,                                    static_cast<int>(bytes));                                                                       launch_kernel(retention_recurrence_reg_kernel<T, D>, dim3(requests, heads, vdim / 32), dim3(32 * parts), bytes, s,                   static_cast<const float*>(qf), static_cast<const float*>(kf), static_cast<const T*>(v), ldv,                           static_cast<const float*>(decay_m1), static_cast<float*>(out), static_cast<float*>(state),                             state_stride, static_cast<const int*>(cu_q), static_cast<const int*>(state_slots), heads, vdim);       } while (0)
+#define PIH_RET_ARGS s, qf, kf, v, ldv, decay_m1, out, state, state_stride, cu_q, state_slots, requests, heads, vdim
 #define PIH_RET(T)                                                                                                     \
   do {                                                                                                                 \
     launch_kernel(retention_prepare_kernel<T>, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s,          \
@@ -254,11 +275,11 @@ extern "C" int pih_retention(int dtype, const void* qk, long long ld, const void
     PIH_LAUNCH_CHECK();                                                                                                \
     if (in_registers) {                                                                                                \
       switch (dim) {                                                                                                   \
-        case 16: PIH_RET_REG(T, 16); break;                                                                            \
-        case 32: PIH_RET_REG(T, 32); break;                                                                            \
-        case 64: PIH_RET_REG(T, 64); break;                                                                            \
-        case 128: PIH_RET_REG(T, 128); break;                                                                          \
-        default: PIH_RET_REG(T, 256); break;                                                                           \
+        case 16: launch_retention_in_registers<T, 16>(PIH_RET_ARGS); break;                                           \
+        case 32: launch_retention_in_registers<T, 32>(PIH_RET_ARGS); break;                                           \
+        case 64: launch_retention_in_registers<T, 64>(PIH_RET_ARGS); break;                                           \
+        case 128: launch_retention_in_registers<T, 128>(PIH_RET_ARGS); break;                                         \
+        default: launch_retention_in_registers<T, 256>(PIH_RET_ARGS); break;                                          \
       }                                                                                                                \
       break;                                                                                                           \
     }                                                                                                                  \
@@ -274,7 +295,7 @@ extern "C" int pih_retention(int dtype, const void* qk, long long ld, const void
   else if (dtype == PIH_BF16) PIH_RET(bf16);
   else return PIH_ERR_BAD_ARGUMENT;
 #undef PIH_RET
-#undef PIH_RET_REG
+#undef PIH_RET_ARGS
   PIH_LAUNCH_CHECK();
   return 0;
 }

@@ -949,7 +949,8 @@ class CudaOps:
                 tile, small = (1 if plan[0] > 0 else 0), (1 if plan[1] > 0 else 0)
             if small:
                 # the rows of small requests: as many parts as bring the warps of the GPU to work
-                splits = max(1, min(32, (148 * 16) // max(1, rows * heads)))
+                # (and no more than leave a part 128 keys of the longest context that the step's tables can hold)
+                splits = max(1, min(32, (148 * 16) // max(1, rows * heads), max(1, plan[2] // 128)))
                 if splits > 1:
                     partial = torch.empty(rows * heads * splits * (4 + 2 * value_dim), dtype=torch.float32, device=qkv.device)
         rc = self.lib.pih_diff_attention(

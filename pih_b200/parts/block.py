@@ -91,7 +91,7 @@ class OutNormBlock:
     def __init__(self, spec, weights, rt: Runtime):
         PreNormBlock.__init__(self, spec, weights, rt)
         for norm in (self.norm_in, self.norm_post):
-            if norm is not None and not hasattr(norm, "weight"):
+            if norm is not None and not hasattr(norm, "weight_f32"):
                 raise TypeError("a norm on a sub-layer's output needs a weight vector")
 
     def _input(self, h, step):
@@ -104,7 +104,7 @@ class OutNormBlock:
 
     def _add(self, h, y, norm, step, bias=None):
         ops = self.rt.ops
-        x = ops.stream_norm_add(h, y, norm.weight, norm.spec.eps, bias=bias,
+        x = ops.stream_norm_add(h, y, norm.weight_f32, norm.spec.eps, bias=bias,
                                 copy_dtype=self.rt.dtype if h.dtype != self.rt.dtype else None)
         step.stream_copy = (h, x) if x is not None else None
 

@@ -29,6 +29,14 @@ class RMSNorm:
         self.spec = spec
         self.rt = rt
         self.weight = bind_vector(weights[getattr(spec, "weight_name", "weight")], rt)
+        self._weight_f32 = None
+
+    @property
+    def weight_f32(self):
+        """The weight in 32-bit (made once), for the kernels that norm a 32-bit stream."""
+        if self._weight_f32 is None:
+            self._weight_f32 = self.weight if self.weight.dtype == torch.float32 else self.weight.float().contiguous()
+        return self._weight_f32
 
     def forward(self, x, rows=None):
         return self.add_forward(x, None, rows=rows)
@@ -37,7 +45,7 @@ class RMSNorm:
         if h.dtype != self.rt.dtype:
             # a residual stream kept in 32-bit beside a 16-bit compute dtype: the sum stays 32-bit, the normed rows
             # take the compute dtype
-            return self.rt.ops.rmsnorm_stream(h, self.weight.float(), self.spec.eps, delta=delta, rows=rows,
+            return self.rt.ops.rmsnorm_stream(h, self.weight_f32, self.spec.eps, delta=delta, rows=rows,
                                               out_dtype=self.rt.dtype)
         return self.rt.ops.rmsnorm(h, self.weight, self.spec.eps, delta=delta, rows=rows)
 

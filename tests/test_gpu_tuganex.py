@@ -169,12 +169,16 @@ def test_row_wise_kernels():
         ref = h.double() + plain.rms_unit(v, 1e-5) * weight.double()
         assert float((hd.double().cpu() - ref).abs().max()) < 1e-5
         assert torch.equal(copy.cpu(), hd.cpu().bfloat16())
-    z = torch.linspace(-6, 6, 1001).view(7, 143)
-    b = torch.randn(143, generator=g) * 0.1
-    got = ops.bias_xielu(z.to(DEV), b.to(DEV), 0.8, 1.3).double().cpu()
-    u = z.double() + b.double()
-    ref = torch.where(u > 0, 0.8 * u * u + 0.5 * u, 1.3 * (torch.expm1(u) - u) + 0.5 * u)
-    assert float((got - ref).abs().max()) < 1e-5
+    for width in (143, 144):                                 # element by element, and 16 bytes a thread
+        z = torch.linspace(-6, 6, 7 * width).view(7, width)
+        b = torch.randn(width, generator=g) * 0.1
+        u = z.double() + b.double()
+        ref = torch.where(u > 0, 0.8 * u * u + 0.5 * u, 1.3 * (torch.expm1(u) - u) + 0.5 * u)
+        assert float((ops.bias_xielu(z.to(DEV), b.to(DEV), 0.8, 1.3).double().cpu() - ref).abs().max()) < 1e-5
+        zb = z.bfloat16()
+        ub = zb.double() + b.double()
+        refb = torch.where(ub > 0, 0.8 * ub * ub + 0.5 * ub, 1.3 * (torch.expm1(ub) - ub) + 0.5 * ub)
+        assert float((ops.bias_xielu(zb.to(DEV), b.to(DEV), 0.8, 1.3).double().cpu() - refb).abs().max()) < 0.2
     gate = torch.randn(rows, 3, generator=g)
     got = ops.add_gated(h.to(DEV), y.to(DEV), gate.to(DEV)[:, 1]).double().cpu()
     assert float((got - (h.double() + torch.sigmoid(gate[:, 1].double())[:, None] * y.double())).abs().max()) < 1e-5
@@ -242,7 +246,7 @@ def _paged(K, V, page, dtype, pages=None):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("dim, vdim, heads, kv_heads", [(16, 24, 4, 2), (64, 64, 2, 1), (32, 128, 6, 6), (128, 128, 2, 1),
-                                                        (24, 40, 2, 2), (12, 20, 3, 1)])
+                                                        (24, 40, 2, 2), (12, 20, 3, 1), (40, 320, 1, 1)])
 @pytest.mark.parametrize("needle", [0, 1, 15, 16, 17, 63, 64, 250, 299])
 def test_differential_attention_finds_one_key_among_hundreds(needle, dim, vdim, heads, kv_heads, dtype):
     """300 cached keys of which ONE matches the query's first map (its score stands out by construction) and another

@@ -43,3 +43,11 @@ def test_top_logprobs_cuts_a_row_into_slices(lib):
     assert slices(64 * 40 * 1024 + 1) == -1
     lib.pih_top_logprobs_scratch_words.restype = ctypes.c_longlong
     assert lib.pih_top_logprobs_scratch_words(3, 151936, 20) == 3 * 8 * 42
+
+
+def test_which_sizes_the_tensor_core_differential_attention_takes(lib):
+    """Key and value sizes that are multiples of 8 up to 128 (smaller ones are padded with zeros in shared memory);
+    everything else runs on the warp kernel."""
+    takes = lib.pih_diff_attention_tile_takes
+    assert takes(64, 128) == 1 and takes(8, 8) == 1 and takes(24, 40) == 1 and takes(128, 128) == 1
+    assert takes(12, 64) == 0 and takes(64, 20) == 0 and takes(136, 64) == 0 and takes(64, 256) == 0
