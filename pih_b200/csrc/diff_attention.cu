@@ -124,14 +124,27 @@ __device__ __forceinline__ void diff_stretch(const float* q, const T* __restrict
       float d1 = 0.0f, d2 = 0.0f;
       constexpr int kVec = 16 / sizeof(T);
       if (dim % kVec == 0 && width % kVec == 0) {           // 16-byte loads; the additions in the same order
-        for (int e = 0; e < dim; e += kVec) {
-          __align__(16) T k1[kVec], k2[kVec];
-          *reinterpret_cast<uint4*>(k1) = *reinterpret_cast<const uint4*>(k + e);
-          *reinterpret_cast<uint4*>(k2) = *reinterpret_cast<const uint4*>(k + dim + e);
+        // four pieces of each map are asked for before the first is used: a lane has up to eight loads in flight
+        for (int e0 = 0; e0 < dim; e0 += 4 * kVec) {
+          uint4 r1[4], r2[4];
 #pragma unroll
-          for (int i = 0; i < kVec; ++i) {
-            d1 = fmaf(q[e + i], to_float<T>(k1[i]), d1);
-            d2 = fmaf(q[dim + e + i], to_float<T>(k2[i]), d2);
+          for (int u = 0; u < 4; ++u) {
+            const int e = min(e0 + u * kVec, dim - kVec);     // (a piece beyond the end: the last one again, not used)
+            r1[u] = *reinterpret_cast<const uint4*>(k + e);
+            r2[u] = *reinterpret_cast<const uint4*>(k + dim + e);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int e = e0 + u * kVec;
+            if (e < dim) {
+              const T* k1 = reinterpret_cast<const T*>(&r1[u]);
+              const T* k2 = reinterpret_cast<const T*>(&r2[u]);
+#pragma unroll
+              for (int i = 0; i < kVec; ++i) {
+                d1 = fmaf(q[e + i], to_float<T>(k1[i]), d1);
+                d2 = fmaf(q[dim + e + i], to_float<T>(k2[i]), d2);
+              }
+            }
           }
         }
       } else {
@@ -154,20 +167,32 @@ __device__ __forceinline__ void diff_stretch(const float* q, const T* __restrict
 #pragma unroll
     for (int e = 0; e < PL; ++e) { a1[e] *= c1; a2[e] *= c2; }
     const long long v_at = at >= 0 ? at + static_cast<long long>(kv_heads) * 2 * dim + static_cast<long long>(g) * vdim : -1;
-    // (no branch on a key without a place: its loads read the cache's first row and count as zeros, so that the loads
-    // of several keys are in flight together)
-#pragma unroll 8
-    for (int jj = 0; jj < 32; ++jj) {
-      const long long va = __shfl_sync(0xffffffffu, v_at, jj);
-      const float w1 = __shfl_sync(0xffffffffu, p1, jj), w2 = __shfl_sync(0xffffffffu, p2, jj);
-      const bool there = va >= 0;
-      const T* v = cache + (there ? va : 0);
+    // The values of kBatch keys are asked for together (a key without a place reads the cache's first row and counts as
+    // zeros): shuffles first, then all loads, then the sums in the keys' order.
+    constexpr int kBatch = PL <= 4 ? 8 : (PL <= 8 ? 4 : 2);
+    for (int j8 = 0; j8 < 32; j8 += kBatch) {
+      long long va[kBatch];
+      float w1[kBatch], w2[kBatch], x[kBatch][PL];
 #pragma unroll
-      for (int e = 0; e < PL; ++e) {
-        if (lane + 32 * e < vdim) {
-          const float x = there ? to_float<T>(v[lane + 32 * e]) : 0.0f;
-          a1[e] = fmaf(w1, x, a1[e]);
-          a2[e] = fmaf(w2, x, a2[e]);
+      for (int b = 0; b < kBatch; ++b) {
+        va[b] = __shfl_sync(0xffffffffu, v_at, j8 + b);
+        w1[b] = __shfl_sync(0xffffffffu, p1, j8 + b);
+        w2[b] = __shfl_sync(0xffffffffu, p2, j8 + b);
+      }
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        const T* v = cache + (va[b] >= 0 ? va[b] : 0);
+#pragma unroll
+        for (int e = 0; e < PL; ++e) x[b][e] = (lane + 32 * e < vdim) ? to_float<T>(v[lane + 32 * e]) : 0.0f;
+      }
+#pragma unroll
+      for (int b = 0; b < kBatch; ++b) {
+        const bool there = va[b] >= 0;
+#pragma unroll
+        for (int e = 0; e < PL; ++e) {
+          const float xv = there ? x[b][e] : 0.0f;
+          a1[e] = fmaf(w1[b], xv, a1[e]);
+          a2[e] = fmaf(w2[b], xv, a2[e]);
         }
       }
     }
