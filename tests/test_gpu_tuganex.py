@@ -458,6 +458,25 @@ def test_retention_rotates_by_the_position_not_by_the_row():
     assert float((a - b).abs().max()) < 2e-3 * float(a.abs().max()) and float(a.abs().max()) > 0.1
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    """Sizes, orders of layers, shared caches and constants drawn at random (odd sizes and sizes that only the plain
+    kernels take among them): a mixed schedule in 32-bit against the plain implementation position by position, and in
+    bfloat16 (every router output chosen) within rounding."""
+    from pih_b200.engine.factory import create_runner
+    raw = tm.random_config(seed)
+    requests = traces.make_requests(raw["vocab"], [70, 45, 33, 18, 1, 2], seed=seed)
+    steps = traces.mixed(requests, seed=seed, max_live=3)
+    for dtype, cfg in (("float32", raw), ("bfloat16", tm.all_chosen(raw))):
+        d = tm.write_model(tmp_path / dtype, cfg, seed=seed, sigma=0.15)
+        _, model, cache, runner = create_runner(d, dtype, page_size=16, max_cache_tokens=traces.peak_tokens(steps, round_to=16),
+                                                max_requests=3)
+        got = traces.replay(runner, steps)
+        model.rt.ops.check_errors()
+        _check(got, tm.plain_logits(d, requests), dtype, f"seed {seed} {dtype}")
+        cache.check()
+
+
 def test_long_decoding(dirs):
     """A short prompt and 300 tokens one by one (pages fill and follow one another; the states run on)."""
     from pih_b200.engine.factory import create_runner

@@ -112,3 +112,50 @@ def plain_logits(model_dir, requests):
             _LOGITS[key] = plain_tuganex.model_layers(cfg, w, toks)[1]
         out[rid] = _LOGITS[key]
     return out
+
+
+def random_config(seed):
+    """A configuration drawn at random: sizes (also odd ones and ones that no fast kernel takes), the order of layers,
+    which layers read whose keys and values, every constant."""
+    import random
+    rnd = random.Random(seed)
+    width = rnd.choice([40, 56, 64, 72, 96, 136])
+    layers, attention_shapes = [], {}
+    for i in range(rnd.randint(3, 7)):
+        if rnd.random() < 0.4:
+            heads = rnd.choice([1, 2, 3, 4])
+            dim = rnd.choice([4, 8, 12, 16, 20, 32, 64])
+            mixer = {"heads": heads, "dim": dim, "vdim": rnd.choice([8, 12, 20, 32, 40, 64, 96]),
+                     "rot": _rot(rnd.choice([d for d in (2, 4, 8, 12, 16, 32, 64) if d <= dim]), rnd.choice([10.0, 1e4, 1e6])),
+                     "decay": [rnd.choice([1.0, 1.0 - 2.0 ** -rnd.randint(1, 10), rnd.uniform(0.3, 0.999)]) for _ in range(heads)]}
+            layer = {"type": "retention", "mixer": mixer}
+        else:
+            sources = [j for j, shape in attention_shapes.items()]
+            if sources and rnd.random() < 0.4:
+                j = rnd.choice(sources)
+                mixer = dict(attention_shapes[j], kv_from=j, heads=attention_shapes[j]["kv_heads"] * rnd.choice([1, 2, 3]),
+                             scale=rnd.uniform(0.1, 0.6), diff=rnd.choice([0.0, 0.2, 0.5, 0.8, -0.3]))
+            else:
+                kv_heads = rnd.choice([1, 2, 3])
+                dim = rnd.choice([4, 8, 12, 16, 24, 32, 40, 64])
+                mixer = _att(kv_heads * rnd.choice([1, 2, 4]), kv_heads, dim, rnd.choice([8, 12, 16, 24, 40, 64, 72, 128, 136]),
+                             _rot(rnd.choice([d for d in (2, 4, 8, 12, 16, 24, 32, 40, 64) if d <= dim]), rnd.choice([10.0, 1e4, 1e6])),
+                             rnd.uniform(0.1, 0.6), rnd.choice([0.0, 0.2, 0.5, 0.8, -0.3]))
+                attention_shapes[i] = {k: mixer[k] for k in ("kv_heads", "dim", "vdim", "rot")}
+            layer = {"type": "attention", "mixer": mixer}
+        kind = rnd.choice(["dense", "moe", "moe", None])
+        if kind == "dense":
+            layer["mlp"] = {"kind": "dense", "ff": rnd.choice([24, 50, 64, 130])}
+        elif kind == "moe":
+            groups = rnd.choice([None, (2, 1), (3, 2), (4, 4), (4, 1)])
+            count = groups[0] if groups else 1
+            outputs = count * rnd.randint(1, 4)
+            identity = rnd.randint(0, outputs - 1)
+            kept = (outputs // count) * (groups[1] if groups else 1)
+            layer["mlp"] = _moe(outputs - identity, identity, rnd.randint(1, kept), rnd.choice([8, 24, 36, 64]), groups=groups,
+                                shared=rnd.choice([None, 16, 40]))
+        else:
+            layer["mlp"] = None
+        layers.append(layer)
+    return {"architecture": "Tuganex", "vocab": rnd.choice([97, 256, 300]), "width": width,
+            "norm": {"eps": rnd.choice([1e-5, 1e-6])}, "layers": layers}
