@@ -44,8 +44,12 @@ class SwiGLU:
 
     def forward(self, x):
         ops = self.rt.ops
-        gate_up = ops.linear(x, self.w_gate_up)
-        act = ops.silu_mul(gate_up, self.interleave)
+        act = None
+        if self.interleave == 8 and x.shape[0] <= getattr(ops, "skinny_max_rows", 0) and hasattr(ops, "linear_skinny"):
+            act = ops.linear_skinny(x, self.w_gate_up, swiglu=True)      # few rows: SiLU-mul in the product's epilogue
+        if act is None:
+            gate_up = ops.linear(x, self.w_gate_up)
+            act = ops.silu_mul(gate_up, self.interleave)
         return ops.linear(act, self.w_down)
 
     def forward_prenorm(self, h, delta, norm):
